@@ -1,0 +1,466 @@
+// Paged attention on tensor cores for bfloat16: one kernel body for prompt portions (many query rows,
+// all keys) and for decoding (few query rows, keys split across warps and across CTAs).
+//
+// Rows of a tile are (token, head-in-group) pairs of ONE kv head of ONE request segment, so a key/value
+// tile fetched through the block table is shared by all query heads of the group.  S = Q K^T and
+// O += P V run on mma.sync m16n8k16 (bf16 in, fp32 accumulate); the running maximum, the sums and the
+// rescaling are 32-bit (online softmax, exp2 of scores pre-multiplied by log2(e)/sqrt(d)).  Keys and
+// values arrive in shared memory by 16-byte cp.async through the page table, double-buffered.
+//
+//   prompt mode  (ROW_WARPS x 1 warps): each warp owns 16 rows and walks every key tile.
+//   decode mode  (1 x KEY_WARPS warps): the warps share 16 rows and each takes a quarter of every key
+//                tile; blockIdx.z additionally splits the keys into ranges of `split_keys`; partial
+//                (max, sum, accumulator) triples are merged in shared memory, and across CTAs by
+//                attn_merge_kernel.  The number of ranges depends on the request's own length only.
+//
+// The head size is a compile-time constant (PI_HEAD_DIM, a multiple of 16 up to 256); the library is
+// built once per head size a model needs.
+//
+// Reference parity: src/ops/kernels/cuda/paged_attention.cu:65-137 (grouping, scale, causal bound by
+// absolute position, online softmax, out = acc / sum, pages with a negative id are skipped).
+#include <math.h>
+
+#include "common.cuh"
+
+#ifndef PI_HEAD_DIM
+#error "compile with -DPI_HEAD_DIM=<multiple of 16>"
+#endif
+static_assert(PI_HEAD_DIM % 16 == 0 && PI_HEAD_DIM >= 16 && PI_HEAD_DIM <= 256, "head size must be 16..256 in steps of 16");
+
+#define BN 64  // keys per tile
+
+struct AttnParams {
+    const bf16* q;        // [T, q_stride] query heads (already normalised and rotated)
+    int q_stride;
+    const bf16* kcache;   // [pages, nkv, page_size, D]
+    const bf16* vcache;
+    const int* block_table;  // [slots, bt_stride]
+    int bt_stride;
+    const int* seg_off;    // [segments] first token (row of q/out) of the segment
+    const int* seg_slot;   // [segments] row of the block table
+    const int* seg_start;  // [segments] absolute position of the segment's first token
+    const int* seg_len;    // [segments] number of tokens
+    bf16* out;             // [T, nq * D]
+    float* part_acc;       // [T * nq, max_splits, D] unnormalised partial outputs (decode mode)
+    float* part_ml;        // [T * nq, max_splits, 2] (max in log2 units, sum)
+    int max_splits;
+    int nq, nkv, group;
+    int page_size;
+    int window;            // 0: all keys
+    float scale_log2;      // log2(e) / sqrt(D)
+    int tiles_per_seg;
+    int split_keys;        // keys per range in decode mode (a multiple of BN)
+    int decode;            // 1: handle segments of one token only; 0: handle the others only
+};
+
+// first key a query at `pos` sees, rounded down to a tile boundary, and the number of key ranges
+__device__ __forceinline__ int window_lo(int pos, int window) {
+    return (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+}
+__device__ __forceinline__ int decode_num_splits(int pos, int window, int split_keys) {
+    const int lo_al = (window_lo(pos, window) / BN) * BN;
+    return (pos + 1 - lo_al + split_keys - 1) / split_keys;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem_ptr) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem_ptr) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);  // .x (low half) = lo
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int D, int ROW_WARPS, int KEY_WARPS>
+__global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(const AttnParams p) {
+    constexpr int BM = ROW_WARPS * 16;
+    constexpr int NTHREADS = ROW_WARPS * KEY_WARPS * 32;
+    constexpr int LDS = D + 8;              // padded row length in elements: conflict-free ldmatrix
+    constexpr int CHUNKS = D / 8;           // 16-byte chunks per row
+    constexpr int KPW = BN / KEY_WARPS;     // keys of a tile that one warp handles
+    constexpr int STAGES = 2;
+    static_assert(KPW % 16 == 0, "a warp needs whole k16 steps");
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                  // [BM][LDS]
+    bf16* Ks = Qs + BM * LDS;                                      // [STAGES][BN][LDS]
+    bf16* Vs = Ks + STAGES * BN * LDS;                             // [STAGES][BN][LDS]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wr = warp / KEY_WARPS, wk = warp % KEY_WARPS;
+    const int seg = blockIdx.x / p.tiles_per_seg, tile = blockIdx.x % p.tiles_per_seg;
+    const int kvh = blockIdx.y, split = blockIdx.z;
+
+    const int len = p.seg_len[seg];
+    if ((len == 1) != (p.decode != 0)) return;
+    const int G = p.group;
+    const int rows_total = len * G;
+    const int row0 = tile * BM;
+    if (row0 >= rows_total) return;
+    const int start = p.seg_start[seg];
+    const int tok_off = p.seg_off[seg];
+    const int* table = p.block_table + (size_t)p.seg_slot[seg] * p.bt_stride;
+
+    const int row_last = (row0 + BM < rows_total ? row0 + BM : rows_total) - 1;
+    const int pos_first = start + row0 / G, pos_last = start + row_last / G;
+    // key range of this CTA: [kbegin, kend), kbegin on a tile boundary
+    int kbegin = (window_lo(pos_first, p.window) / BN) * BN;
+    int kend = pos_last + 1;
+    int nsplits = 1;
+    if (p.decode) {
+        nsplits = decode_num_splits(pos_first, p.window, p.split_keys);
+        if (split >= nsplits) return;
+        kbegin += split * p.split_keys;
+        if (kbegin + p.split_keys < kend) kend = kbegin + p.split_keys;
+    } else if (split > 0) {
+        return;
+    }
+    const int num_tiles = (kend - kbegin + BN - 1) / BN;
+
+    // ---- loaders -----------------------------------------------------------------------------------
+    auto load_q = [&]() {
+        for (int idx = tid; idx < BM * CHUNKS; idx += NTHREADS) {
+            const int r = idx / CHUNKS, c = idx % CHUNKS;
+            const int rf = row0 + r;
+            const bool valid = rf < rows_total;
+            const int tok = valid ? rf / G : 0, h = valid ? rf % G : 0;
+            const bf16* src = p.q + (size_t)(tok_off + tok) * p.q_stride + (size_t)(kvh * G + h) * D + c * 8;
+            cp_async16(Qs + r * LDS + c * 8, src, valid);
+        }
+    };
+    auto load_kv = [&](int kt, int stage) {
+        const int k0 = kbegin + kt * BN;
+        bf16* kd = Ks + stage * BN * LDS;
+        bf16* vd = Vs + stage * BN * LDS;
+        for (int idx = tid; idx < BN * CHUNKS; idx += NTHREADS) {
+            const int r = idx / CHUNKS, c = idx % CHUNKS;
+            const int j = k0 + r;
+            bool valid = j < kend;
+            size_t off = 0;
+            if (valid) {
+                const int page = table[j / p.page_size];
+                valid = page >= 0;
+                if (valid) off = (((size_t)page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * D + c * 8;
+            }
+            cp_async16(kd + r * LDS + c * 8, p.kcache + off, valid);
+            cp_async16(vd + r * LDS + c * 8, p.vcache + off, valid);
+        }
+    };
+
+    // ---- per-thread row bookkeeping ------------------------------------------------------------------
+    const int g = lane >> 2, tq = lane & 3;
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int rf = row0 + wr * 16 + g + 8 * i;
+        if (rf < rows_total) {
+            pos_r[i] = start + rf / G;
+            lo_r[i] = window_lo(pos_r[i], p.window);
+        } else {
+            pos_r[i] = -1;  // no key is visible
+            lo_r[i] = 0;
+        }
+    }
+    // visibility bounds of the whole warp (uniform): used to skip tiles
+    const int wrow_first = row0 + wr * 16;
+    int warp_pos_max = -1, warp_lo_min = 0;
+    if (wrow_first < rows_total) {
+        const int wrow_last = (wrow_first + 15 < rows_total ? wrow_first + 15 : rows_total - 1);
+        warp_pos_max = start + wrow_last / G;
+        warp_lo_min = window_lo(start + wrow_first / G, p.window);
+    }
+
+    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = 0.0f; o[i][1] = 0.0f; o[i][2] = 0.0f; o[i][3] = 0.0f; }
+
+    // ---- pipeline ------------------------------------------------------------------------------------
+    load_q();
+    load_kv(0, 0);
+    cp_async_commit();
+
+    for (int kt = 0; kt < num_tiles; ++kt) {
+        cp_async_wait<0>();
+        __syncthreads();  // tile kt (and Q) visible to all; everyone is done with the other stage
+        if (kt + 1 < num_tiles) load_kv(kt + 1, (kt + 1) % STAGES);
+        cp_async_commit();
+
+        const int stage = kt % STAGES;
+        const bf16* ks = Ks + stage * BN * LDS;
+        const bf16* vs = Vs + stage * BN * LDS;
+        const int kw0 = kbegin + kt * BN + wk * KPW;  // first key of this warp's share
+        if (kw0 > warp_pos_max || kw0 + KPW - 1 < warp_lo_min) continue;  // nothing visible (uniform per warp)
+
+        // S = Q K^T for 16 rows x KPW keys
+        float s[KPW / 8][4];
+#pragma unroll
+        for (int i = 0; i < KPW / 8; ++i) { s[i][0] = 0.0f; s[i][1] = 0.0f; s[i][2] = 0.0f; s[i][3] = 0.0f; }
+#pragma unroll
+        for (int ks16 = 0; ks16 < D / 16; ++ks16) {
+            unsigned a[4];
+            ldmatrix_x4(a, Qs + (wr * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks16 * 16 + 8 * (lane >> 4));
+#pragma unroll
+            for (int np = 0; np < KPW / 16; ++np) {
+                unsigned b[4];
+                ldmatrix_x4(b, ks + (wk * KPW + np * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + ks16 * 16 + 8 * ((lane >> 3) & 1));
+                mma_bf16(s[2 * np], a, b[0], b[1]);
+                mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+
+        // mask, scale, running maximum
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < KPW / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int j = kw0 + nt * 8 + 2 * tq + (e & 1);
+                const bool visible = j <= pos_r[i] && j >= lo_r[i] && j < kend;
+                const float v = visible ? s[nt][e] * p.scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mx[i] = fmaxf(mx[i], v);
+            }
+        }
+        float alpha[2], base[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_r[i], mx[i]);
+            base[i] = (m_new == -INFINITY) ? 0.0f : m_new;
+            alpha[i] = exp2f(m_r[i] - base[i]);
+            m_r[i] = m_new;
+        }
+        float rs[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int nt = 0; nt < KPW / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[nt][e] - base[e >> 1]);
+                s[nt][e] = pv;
+                rs[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) l_r[i] = l_r[i] * alpha[i] + rs[i];  // quad partial; summed at the end
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            o[dt][0] *= alpha[0]; o[dt][1] *= alpha[0];
+            o[dt][2] *= alpha[1]; o[dt][3] *= alpha[1];
+        }
+
+        // O += P V
+#pragma unroll
+        for (int kp = 0; kp < KPW / 16; ++kp) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * kp][0], s[2 * kp][1]);
+            a[1] = pack_bf16(s[2 * kp][2], s[2 * kp][3]);
+            a[2] = pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]);
+            a[3] = pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < D / 16; ++dp) {
+                unsigned b[4];
+                ldmatrix_x4_trans(b, vs + (wk * KPW + kp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+                mma_bf16(o[2 * dp], a, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // quad-wide sums
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 1);
+        l_r[i] += __shfl_xor_sync(0xffffffffu, l_r[i], 2);
+    }
+
+    if (KEY_WARPS == 1) {
+        // each warp owns its rows: write them out (prompt mode never splits)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int rf = row0 + wr * 16 + g + 8 * i;
+            if (rf >= rows_total) continue;
+            const int tok = rf / G, h = rf % G;
+            const float inv = l_r[i] > 0.0f ? 1.0f / l_r[i] : 0.0f;
+            bf16* orow = p.out + (size_t)(tok_off + tok) * p.nq * D + (size_t)(kvh * G + h) * D;
+#pragma unroll
+            for (int dt = 0; dt < D / 8; ++dt)
+                *reinterpret_cast<unsigned*>(orow + dt * 8 + 2 * tq) = pack_bf16(o[dt][2 * i] * inv, o[dt][2 * i + 1] * inv);
+        }
+        return;
+    }
+
+    // decode mode: merge the KEY_WARPS partial results of the 16 shared rows through shared memory
+    __syncthreads();  // everyone is done reading K/V tiles
+    float* mo = reinterpret_cast<float*>(Ks);        // [KEY_WARPS][16][D]
+    float* mm = mo + KEY_WARPS * 16 * D;             // [KEY_WARPS][16]
+    float* ml = mm + KEY_WARPS * 16;                 // [KEY_WARPS][16]
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = g + 8 * i;
+        float* dst = mo + (wk * 16 + r) * D;
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            dst[dt * 8 + 2 * tq] = o[dt][2 * i];
+            dst[dt * 8 + 2 * tq + 1] = o[dt][2 * i + 1];
+        }
+        if (tq == 0) { mm[wk * 16 + r] = m_r[i]; ml[wk * 16 + r] = l_r[i]; }
+    }
+    __syncthreads();
+    const int valid_rows = rows_total - row0 < 16 ? rows_total - row0 : 16;
+    for (int idx = tid; idx < valid_rows * D; idx += NTHREADS) {
+        const int r = idx / D, e = idx % D;
+        float mstar = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < KEY_WARPS; ++w) mstar = fmaxf(mstar, mm[w * 16 + r]);
+        float lsum = 0.0f, acc = 0.0f;
+        if (mstar != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < KEY_WARPS; ++w) {
+                const float f = exp2f(mm[w * 16 + r] - mstar);
+                lsum += ml[w * 16 + r] * f;
+                acc += mo[(w * 16 + r) * D + e] * f;
+            }
+        }
+        const int rf = row0 + r;
+        const int tok = rf / G, h = rf % G;
+        const size_t orow = (size_t)(tok_off + tok) * p.nq + (size_t)(kvh * G + h);
+        if (nsplits == 1) {
+            p.out[orow * D + e] = __float2bfloat16_rn(lsum > 0.0f ? acc / lsum : 0.0f);
+        } else {
+            p.part_acc[(orow * p.max_splits + split) * D + e] = acc;
+            if (e == 0) {
+                p.part_ml[(orow * p.max_splits + split) * 2] = mstar;
+                p.part_ml[(orow * p.max_splits + split) * 2 + 1] = lsum;
+            }
+        }
+    }
+}
+
+// Combine the key ranges of decode-mode rows: one block per (token, head).
+template <int D>
+__global__ void attn_merge_kernel(const AttnParams p, const int* __restrict__ token_seg) {
+    const int row = blockIdx.x;  // token * nq + head
+    const int t = row / p.nq;
+    const int seg = token_seg[t];
+    if (p.seg_len[seg] != 1) return;
+    const int n = decode_num_splits(p.seg_start[seg], p.window, p.split_keys);
+    if (n <= 1) return;
+    const float* ml = p.part_ml + (size_t)row * p.max_splits * 2;
+    const float* acc = p.part_acc + (size_t)row * p.max_splits * D;
+    float mstar = -INFINITY;
+    for (int s = 0; s < n; ++s) mstar = fmaxf(mstar, ml[2 * s]);
+    for (int e = threadIdx.x; e < D; e += blockDim.x) {
+        float lsum = 0.0f, a = 0.0f;
+        if (mstar != -INFINITY) {
+            for (int s = 0; s < n; ++s) {
+                const float f = exp2f(ml[2 * s] - mstar);
+                lsum += ml[2 * s + 1] * f;
+                a += acc[(size_t)s * D + e] * f;
+            }
+        }
+        p.out[(size_t)row * D + e] = __float2bfloat16_rn(lsum > 0.0f ? a / lsum : 0.0f);
+    }
+}
+
+template <int ROW_WARPS, int KEY_WARPS>
+static size_t attn_smem_bytes() {
+    return (size_t)(ROW_WARPS * 16 + 2 * 2 * BN) * (PI_HEAD_DIM + 8) * sizeof(bf16);
+}
+
+template <int ROW_WARPS, int KEY_WARPS>
+static int launch_attn(const AttnParams& p, int num_segments, int splits, cudaStream_t stream) {
+    static bool configured = false;  // once per process and kernel
+    const size_t smem = attn_smem_bytes<ROW_WARPS, KEY_WARPS>();
+    auto kernel = attn_mma_kernel<PI_HEAD_DIM, ROW_WARPS, KEY_WARPS>;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) {
+            snprintf(g_pi_error, sizeof(g_pi_error), "attention: cannot reserve %zu bytes of shared memory: %s", smem,
+                     cudaGetErrorString(err));
+            return (int)err;
+        }
+        configured = true;
+    }
+    dim3 grid((unsigned)num_segments * p.tiles_per_seg, p.nkv, splits);
+    kernel<<<grid, ROW_WARPS * KEY_WARPS * 32, smem, stream>>>(p);
+    return pi_check_launch("pi_attention_mma");
+}
+
+PI_EXPORT int pi_attention_head_dim() { return PI_HEAD_DIM; }
+
+// The number of key ranges a decoding request at position `pos` (0-based, its newest token) uses.
+PI_EXPORT int pi_attention_num_splits(int pos, int window, int split_keys) {
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo_al = (lo / BN) * BN;
+    return (pos + 1 - lo_al + split_keys - 1) / split_keys;
+}
+
+// has_prompt / has_decode say which kinds of segment the batch holds (a kernel is launched for each kind
+// present); max_seg_len bounds the grid of the prompt kernel; max_splits is the width of the scratch and the
+// grid depth of the decode kernel (>= the number of ranges of every decoding request in the batch).
+PI_EXPORT int pi_attention_mma(const void* q, int q_stride, const void* kcache, const void* vcache,
+                               const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                               const int* seg_start, const int* seg_len, const int* token_seg, void* out,
+                               float* part_acc, float* part_ml, int max_splits, int split_keys, int num_tokens,
+                               int num_segments, int max_seg_len, int has_prompt, int has_decode, int nq, int nkv,
+                               int page_size, int window, float scale, cudaStream_t stream) {
+    if (num_tokens <= 0 || num_segments <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return pi_refuse("pi_attention_mma: nq=%d must be a positive multiple of nkv=%d", nq, nkv);
+    if (page_size <= 0) return pi_refuse("pi_attention_mma: page_size=%d must be positive", page_size);
+    if (q_stride % 8 != 0) return pi_refuse("pi_attention_mma: q_stride=%d must be a multiple of 8 elements", q_stride);
+    if (split_keys <= 0 || split_keys % BN != 0) return pi_refuse("pi_attention_mma: split_keys=%d must be a positive multiple of %d", split_keys, BN);
+    if (nkv > 65535 || max_splits > 65535) return pi_refuse("pi_attention_mma: nkv=%d or max_splits=%d beyond the grid limit", nkv, max_splits);
+    AttnParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride;
+    p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.seg_off = seg_off; p.seg_slot = seg_slot; p.seg_start = seg_start; p.seg_len = seg_len;
+    p.out = (bf16*)out; p.part_acc = part_acc; p.part_ml = part_ml; p.max_splits = max_splits;
+    p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.page_size = page_size; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.split_keys = split_keys;
+    int rc = 0;
+    if (has_prompt) {
+        constexpr int BM = 4 * 16;
+        p.decode = 0;
+        p.tiles_per_seg = (int)(((long long)max_seg_len * p.group + BM - 1) / BM);
+        rc = launch_attn<4, 1>(p, num_segments, 1, stream);
+        if (rc) return rc;
+    }
+    if (has_decode) {
+        if (max_splits < 1) return pi_refuse("pi_attention_mma: max_splits=%d must be at least 1", max_splits);
+        if (max_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return pi_refuse("pi_attention_mma: scratch for %d key ranges is missing", max_splits);
+        p.decode = 1;
+        p.tiles_per_seg = (p.group + 15) / 16;
+        rc = launch_attn<1, 4>(p, num_segments, max_splits, stream);
+        if (rc) return rc;
+        if (max_splits > 1) {
+            attn_merge_kernel<PI_HEAD_DIM><<<num_tokens * nq, PI_HEAD_DIM >= 128 ? 128 : 64, 0, stream>>>(p, token_seg);
+            rc = pi_check_launch("pi_attention_mma merge");
+        }
+    }
+    return rc;
+}

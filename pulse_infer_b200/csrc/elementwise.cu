@@ -1,0 +1,321 @@
+// Memory-bound kernels of the step: embedding gather, fused residual-add + RMSNorm, SiLU*mul,
+// rotation tables, and the fused per-head RMSNorm + rotation + paged key/value write.
+//
+// Formulas follow the reference engine (paths inside its project):
+//   embedding       src/ops/kernels/cuda/embedding_kernel.cu:7-28   (row gather; an id outside the table gives zeros)
+//   RMSNorm         src/ops/kernels/cuda/rmsnorm_kernel.cu:97-118,147 (x * rsqrt(mean(x^2) + eps) * w, float math)
+//   rotation        src/ops/kernels/cuda/rope_kernel.cu:102-123     (angle = pos / theta^(2i/rot), adjacent pairs)
+//   paged write     src/ops/kernels/cuda/paged_kv_write.cu:35-52    (page = table[pos / page], slot = pos % page)
+//   SiLU, product   src/ops/kernels/cuda/silu_kernel.cu:78-104, mul_kernel.cu:38-46
+// Differences by design: the residual stream is 32-bit, one rounding per fused kernel instead of one per
+// reference op, exact expf/sqrtf (the reference builds with fast-math), rotation angles from a table that
+// is computed once per step in 64-bit.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------------
+// embedding: out[t, :] = table[token[t], :] as 32-bit residual
+// ---------------------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out,
+                             int hidden, int vocab) {
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    const bool valid = id >= 0 && id < vocab;
+    const TW* src = table + (size_t)(valid ? id : 0) * hidden;
+    float* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = valid ? to_float<TW>(src[i]) : 0.0f;
+}
+
+PI_EXPORT int pi_embed(const int* tokens, const void* table, int table_dtype, float* out, int num_tokens, int hidden,
+                       int vocab, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0) return pi_refuse("pi_embed: hidden=%d vocab=%d must be positive", hidden, vocab);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == PI_BF16)
+        embed_kernel<bf16><<<num_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, hidden, vocab);
+    else if (table_dtype == PI_F32)
+        embed_kernel<float><<<num_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
+    else
+        return pi_refuse("pi_embed: unknown table dtype code %d", table_dtype);
+    return pi_check_launch("pi_embed");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// fused residual add + RMSNorm
+//   rows == nullptr:  h[r] += delta[r] (stored), x[r] = norm(h[r])                    for r in [0, n)
+//   rows != nullptr:  x[i] = norm(h[rows[i]] + delta[rows[i]])   (h is left untouched) for i in [0, n)
+// One block per row; the sum of squares, the inverse root and the product are 32-bit.
+// ---------------------------------------------------------------------------------------------------
+template <typename TA, typename TW, int VEC>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__ delta, const TW* __restrict__ w,
+                                   TA* __restrict__ x, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int out_row = blockIdx.x;
+    const int src_row = rows ? rows[out_row] : out_row;
+    float* hr = h + (size_t)src_row * hidden;
+    const TA* dr = delta ? delta + (size_t)src_row * hidden : nullptr;
+    TA* xr = x + (size_t)out_row * hidden;
+    const bool store_h = (rows == nullptr) && (delta != nullptr);
+
+    float ss = 0.0f;
+    for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
+        float v[VEC];
+        if (VEC == 4) {
+            const float4 hv = *reinterpret_cast<const float4*>(hr + i);
+            v[0] = hv.x; v[1 % VEC] = hv.y; v[2 % VEC] = hv.z; v[3 % VEC] = hv.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[k] = hr[i + k];
+        }
+        if (dr) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[k] += to_float<TA>(dr[i + k]);
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) ss += v[k] * v[k];
+        if (store_h) {
+            if (VEC == 4) {
+                *reinterpret_cast<float4*>(hr + i) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) hr[i + k] = v[k];
+            }
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+
+    // second pass: every thread re-reads exactly the elements it wrote (or read) above
+    const bool readd = (dr != nullptr) && !store_h;
+    for (int i = threadIdx.x * VEC; i < hidden; i += blockDim.x * VEC) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            float v = hr[i + k];
+            if (readd) v += to_float<TA>(dr[i + k]);
+            xr[i + k] = from_float<TA>(v * inv * to_float<TW>(w[i + k]));
+        }
+    }
+}
+
+template <typename TA, typename TW>
+static void launch_add_rmsnorm(float* h, const void* delta, const void* w, void* x, const int* rows, int n, int hidden,
+                               float eps, cudaStream_t stream) {
+    const int threads = hidden >= 2048 ? 256 : 128;
+    if (hidden % 4 == 0)
+        add_rmsnorm_kernel<TA, TW, 4><<<n, threads, 0, stream>>>(h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps);
+    else
+        add_rmsnorm_kernel<TA, TW, 1><<<n, threads, 0, stream>>>(h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps);
+}
+
+PI_EXPORT int pi_add_rmsnorm(float* h, const void* delta, const void* weight, int weight_dtype, void* x, int act_dtype,
+                             const int* rows, int n, int hidden, float eps, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (hidden <= 0) return pi_refuse("pi_add_rmsnorm: hidden=%d must be positive", hidden);
+    if (act_dtype == PI_BF16 && weight_dtype == PI_BF16) launch_add_rmsnorm<bf16, bf16>(h, delta, weight, x, rows, n, hidden, eps, stream);
+    else if (act_dtype == PI_BF16 && weight_dtype == PI_F32) launch_add_rmsnorm<bf16, float>(h, delta, weight, x, rows, n, hidden, eps, stream);
+    else if (act_dtype == PI_F32 && weight_dtype == PI_F32) launch_add_rmsnorm<float, float>(h, delta, weight, x, rows, n, hidden, eps, stream);
+    else if (act_dtype == PI_F32 && weight_dtype == PI_BF16) launch_add_rmsnorm<float, bf16>(h, delta, weight, x, rows, n, hidden, eps, stream);
+    else return pi_refuse("pi_add_rmsnorm: unknown dtype codes act=%d weight=%d", act_dtype, weight_dtype);
+    return pi_check_launch("pi_add_rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// SiLU(gate) * up on the fused [n, 2*inter] output of the gate_up product: out[n, inter]
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const size_t row = e / inter;
+    const int col = (int)(e % inter);
+    const float g = to_float<T>(gu[row * 2 * (size_t)inter + col]);
+    const float u = to_float<T>(gu[row * 2 * (size_t)inter + inter + col]);
+    out[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+// 8 elements (bf16) or 4 (float) per thread with 16-byte accesses; needs inter % VEC == 0
+template <typename T, int VEC>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs) {
+    struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total_vecs) return;
+    const int vecs_per_row = inter / VEC;
+    const size_t row = idx / vecs_per_row;
+    const int col = (int)(idx % vecs_per_row) * VEC;
+    const Pack g = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + col);
+    const Pack u = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + inter + col);
+    Pack o;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        const float gv = to_float<T>(g.v[k]);
+        o.v[k] = from_float<T>(gv / (1.0f + expf(-gv)) * to_float<T>(u.v[k]));
+    }
+    *reinterpret_cast<Pack*>(out + row * (size_t)inter + col) = o;
+}
+
+PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (inter <= 0) return pi_refuse("pi_silu_mul: inter=%d must be positive", inter);
+    const size_t total = (size_t)n * inter;
+    const int threads = 256;
+    if (dtype == PI_BF16 && inter % 8 == 0) {
+        const size_t vecs = total / 8;
+        silu_mul_vec_kernel<bf16, 8><<<(unsigned)((vecs + threads - 1) / threads), threads, 0, stream>>>(
+            (const bf16*)gate_up, (bf16*)out, inter, vecs);
+    } else if (dtype == PI_F32 && inter % 4 == 0) {
+        const size_t vecs = total / 4;
+        silu_mul_vec_kernel<float, 4><<<(unsigned)((vecs + threads - 1) / threads), threads, 0, stream>>>(
+            (const float*)gate_up, (float*)out, inter, vecs);
+    } else if (dtype == PI_BF16 || dtype == PI_F32) {
+        // widths that are no multiple of the vector: rows may start unaligned, so plain element accesses
+        const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+        if (dtype == PI_BF16) silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+        else silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    } else {
+        return pi_refuse("pi_silu_mul: unknown dtype code %d", dtype);
+    }
+    return pi_check_launch("pi_silu_mul");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// rotation tables for one step: cos/sin of pos[t] / divisor[i], angle in 64-bit, stored as 32-bit
+// ---------------------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ divisors,
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int num_tokens, int pairs) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= num_tokens * pairs) return;
+    const int t = idx / pairs, i = idx % pairs;
+    const double angle = (double)positions[t] / divisors[i];
+    double s, c;
+    sincos(angle, &s, &c);
+    cos_out[idx] = (float)c;
+    sin_out[idx] = (float)s;
+}
+
+PI_EXPORT int pi_rope_table(const int* positions, const double* divisors, float* cos_out, float* sin_out, int num_tokens,
+                            int pairs, cudaStream_t stream) {
+    if (num_tokens <= 0 || pairs <= 0) return 0;
+    const int total = num_tokens * pairs, threads = 128;
+    rope_table_kernel<<<(total + threads - 1) / threads, threads, 0, stream>>>(positions, divisors, cos_out, sin_out,
+                                                                               num_tokens, pairs);
+    return pi_check_launch("pi_rope_table");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// fused per-head RMSNorm + rotation + paged key/value write.
+// Input: qkv [T, row_stride] holding nq query heads, then nkv key heads, then nkv value heads, each of width d.
+// One warp per (token, head):
+//   query head: normalise (weight qw), rotate, write back in place
+//   key head:   normalise (weight kw), rotate, write into K page
+//   value head: copy into V page
+// pairing: 1 = adjacent pairs (2i, 2i+1) as the reference computes; 0 = split halves (i, i + rot/2).
+// Elements at and beyond rot (partial rotation) are normalised but not rotated.
+// A token whose page id is negative is skipped and counted in *error_count.
+// ---------------------------------------------------------------------------------------------------
+#define QK_MAX_PAIRS 4  // pairs per lane: head_dim up to 256
+
+template <typename TA, typename TW>
+__global__ void qk_norm_rope_write_kernel(TA* __restrict__ qkv, int row_stride, const TW* __restrict__ qw,
+                                          const TW* __restrict__ kw, float eps, int has_norm,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_pairs,
+                                          int adjacent, TA* __restrict__ kcache, TA* __restrict__ vcache,
+                                          const int* __restrict__ block_table, int bt_stride,
+                                          const int* __restrict__ token_slot, const int* __restrict__ positions,
+                                          int page_size, int nq, int nkv, int d, int* __restrict__ error_count) {
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+    if (head >= nq + 2 * nkv) return;
+    TA* src = qkv + (size_t)t * row_stride + (size_t)head * d;
+
+    TA* dst = src;  // query heads are rewritten in place
+    if (head >= nq) {
+        const int kvh = (head - nq) % nkv;
+        const int pos = positions[t];
+        const int page = block_table[(size_t)token_slot[t] * bt_stride + pos / page_size];
+        if (page < 0) {
+            if (lane == 0) atomicAdd(error_count, 1);
+            return;
+        }
+        TA* base = (head < nq + nkv) ? kcache : vcache;
+        dst = base + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * d;
+    }
+
+    if (head >= nq + nkv) {  // value head: plain copy
+        for (int e = lane; e < d; e += 32) dst[e] = src[e];
+        return;
+    }
+
+    const TW* w = head < nq ? qw : kw;
+    const int half_pairs = d / 2;
+    float x0[QK_MAX_PAIRS], x1[QK_MAX_PAIRS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < QK_MAX_PAIRS; ++k) {
+        const int p = lane + 32 * k;
+        x0[k] = 0.0f; x1[k] = 0.0f;
+        if (p < half_pairs) {
+            int i0, i1;
+            if (p < rot_pairs && !adjacent) { i0 = p; i1 = p + rot_pairs; }
+            else { i0 = 2 * p; i1 = 2 * p + 1; }
+            x0[k] = to_float<TA>(src[i0]);
+            x1[k] = to_float<TA>(src[i1]);
+            ss += x0[k] * x0[k] + x1[k] * x1[k];
+        }
+    }
+    float inv = 1.0f;
+    if (has_norm) {
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    // all loads of this head are done before any store (in-place rewrite of query heads)
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < QK_MAX_PAIRS; ++k) {
+        const int p = lane + 32 * k;
+        if (p < half_pairs) {
+            int i0, i1;
+            if (p < rot_pairs && !adjacent) { i0 = p; i1 = p + rot_pairs; }
+            else { i0 = 2 * p; i1 = 2 * p + 1; }
+            float v0 = x0[k], v1 = x1[k];
+            if (has_norm) {
+                v0 = v0 * inv * to_float<TW>(w[i0]);
+                v1 = v1 * inv * to_float<TW>(w[i1]);
+            }
+            if (p < rot_pairs) {
+                const float c = cos_t[(size_t)t * rot_pairs + p], s = sin_t[(size_t)t * rot_pairs + p];
+                const float r0 = v0 * c - v1 * s;
+                const float r1 = v0 * s + v1 * c;
+                v0 = r0; v1 = r1;
+            }
+            dst[i0] = from_float<TA>(v0);
+            dst[i1] = from_float<TA>(v1);
+        }
+    }
+}
+
+PI_EXPORT int pi_qk_norm_rope_write(void* qkv, int row_stride, int act_dtype, const void* q_weight, const void* k_weight,
+                                    int weight_dtype, float eps, int has_norm, const float* cos_t, const float* sin_t,
+                                    int rot_pairs, int adjacent, void* kcache, void* vcache, const int* block_table,
+                                    int bt_stride, const int* token_slot, const int* positions, int page_size, int nq,
+                                    int nkv, int d, int num_tokens, int* error_count, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (d <= 0 || d % 2 != 0 || d > 64 * QK_MAX_PAIRS)
+        return pi_refuse("pi_qk_norm_rope_write: head_dim=%d must be even and at most %d", d, 64 * QK_MAX_PAIRS);
+    if (rot_pairs < 0 || rot_pairs * 2 > d) return pi_refuse("pi_qk_norm_rope_write: rotary width %d exceeds head_dim %d", rot_pairs * 2, d);
+    if (nq < 0 || nkv < 0 || nq + nkv == 0) return pi_refuse("pi_qk_norm_rope_write: nq=%d nkv=%d", nq, nkv);
+    if (nkv > 0 && page_size <= 0) return pi_refuse("pi_qk_norm_rope_write: page_size=%d must be positive", page_size);
+    const int warps = 4;
+    dim3 grid(num_tokens, (nq + 2 * nkv + warps - 1) / warps);
+#define QK_LAUNCH(TA, TW)                                                                                              \
+    qk_norm_rope_write_kernel<TA, TW><<<grid, warps * 32, 0, stream>>>(                                                 \
+        (TA*)qkv, row_stride, (const TW*)q_weight, (const TW*)k_weight, eps, has_norm, cos_t, sin_t, rot_pairs, adjacent, \
+        (TA*)kcache, (TA*)vcache, block_table, bt_stride, token_slot, positions, page_size, nq, nkv, d, error_count)
+    if (act_dtype == PI_BF16 && weight_dtype == PI_BF16) QK_LAUNCH(bf16, bf16);
+    else if (act_dtype == PI_BF16 && weight_dtype == PI_F32) QK_LAUNCH(bf16, float);
+    else if (act_dtype == PI_F32 && weight_dtype == PI_F32) QK_LAUNCH(float, float);
+    else if (act_dtype == PI_F32 && weight_dtype == PI_BF16) QK_LAUNCH(float, bf16);
+    else return pi_refuse("pi_qk_norm_rope_write: unknown dtype codes act=%d weight=%d", act_dtype, weight_dtype);
+#undef QK_LAUNCH
+    return pi_check_launch("pi_qk_norm_rope_write");
+}

@@ -1,0 +1,67 @@
+"""Putting an engine together: configuration -> model -> weights -> cache -> step function."""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .. import ops
+from ..cache import CacheManager
+from ..config.registry import get_architecture, load_config
+from ..parts.model import DecoderModel, Runtime
+from ..weights import init_random_weights, load_weights
+from .step import ModelRunner
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("pulse_infer_b200 runs on a CUDA device (sm_100a) only; there is no CPU path. "
+                           f"Asked for '{device}', torch.cuda.is_available() = {torch.cuda.is_available()}")
+    return device
+
+
+def build_model(config, runtime: Runtime, **spec_options) -> DecoderModel:
+    arch = get_architecture(config.architecture)
+    return DecoderModel(arch.build_spec(config, **spec_options), runtime)
+
+
+def head_dims_of(model: DecoderModel) -> list:
+    dims = set()
+    for cs in model.cache_specs():
+        if cs is not None and cs.head_dim % 16 == 0 and cs.head_dim <= 256:
+            dims.add(cs.head_dim)
+    return sorted(dims)
+
+
+def build_runner(model_dir: str | None = None, *, config=None, seed: int | None = None, dtype: str = "bfloat16",
+                 device="cuda:0", page_size: int = 16, num_pages: int | None = None, max_tokens: int | None = None,
+                 max_requests: int = 64, max_tokens_per_request: int | None = None,
+                 max_tokens_per_step: int | None = None, attention_impl: str = "auto", **spec_options) -> ModelRunner:
+    """From a model folder (``model_dir``) or from a configuration plus a seed (random weights on the
+    device) to a ready step function.  The page pool holds ``num_pages`` pages per layer group, or
+    enough for ``max_tokens`` tokens."""
+    device = require_cuda(device)
+    runtime = Runtime(device, dtype, attention_impl)
+    if model_dir is not None:
+        config = load_config(model_dir)
+    elif config is None:
+        raise ValueError("give a model folder or a configuration")
+    model = build_model(config, runtime, **spec_options)
+    ops.preload(head_dims_of(model) if runtime.mode == "bfloat16" and attention_impl != "simple" else ())
+    with torch.cuda.device(device):
+        if model_dir is not None:
+            load_weights(model, model_dir, runtime)
+        else:
+            init_random_weights(model, 0 if seed is None else seed, runtime,
+                                "bfloat16" if runtime.mode == "bfloat16" else "float32")
+        if num_pages is None:
+            if max_tokens is None:
+                raise ValueError("give num_pages or max_tokens to size the page pool")
+            num_pages = (max_tokens + page_size - 1) // page_size
+        per_request = max_tokens_per_request or min(model.spec.max_position, num_pages * page_size)
+        cache = CacheManager(model.cache_specs(), model.state_specs(), page_size, num_pages, max_requests,
+                             per_request, dtype=runtime.act_dtype, device=device)
+    runner = ModelRunner(model, cache, runtime, max_tokens_per_step)
+    runner.config = config
+    return runner

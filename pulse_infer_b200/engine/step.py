@@ -1,0 +1,89 @@
+"""The step function: ONE entry point that runs a batch of (request, its next tokens) through the
+model from the cache and returns the logits at the wanted places.
+
+A batch may mix portions of prompts of any length with single decoded tokens.  Only the tokens given
+are computed; everything earlier comes from the pages that earlier steps filled.  Pages are reserved
+before the model runs (so a step either has all its pages or does not start) and lengths are
+committed after it.
+
+Reference parity: ``src/model/qwen3/model.cpp:1179-1374`` (``forward_batched``) - same inputs in spirit
+(tokens, absolute positions, sequence ids), but the reference allocates pages while walking the tokens
+(``model.cpp:1204-1250``), reallocates its workspaces when the token count changes (``model.cpp:467-587``)
+and returns logits for every row.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheManager
+from .context import Segment, StepContext
+
+
+class StepError(ValueError):
+    pass
+
+
+class ModelRunner:
+    def __init__(self, model, cache_manager: CacheManager, runtime, max_tokens_per_step: int | None = None):
+        self.model = model
+        self.cache = cache_manager
+        self.runtime = runtime
+        self.max_tokens_per_step = max_tokens_per_step
+        self.vocab_size = model.spec.vocab_size
+        self.max_position = model.spec.max_position
+        self._last_ctx: StepContext | None = None
+
+    # ---- requests ------------------------------------------------------------------------------------
+    def open(self, request_id) -> int:
+        return self.cache.open(request_id)
+
+    def close(self, request_id) -> None:
+        self.cache.close(request_id)
+
+    # ---- the step ---------------------------------------------------------------------------------------
+    def prepare(self, segments: list) -> None:
+        """Validate the batch, resolve slots and start positions, reserve pages."""
+        if not segments:
+            raise StepError("a step needs at least one segment")
+        seen = set()
+        total = 0
+        for s in segments:
+            if s.request_id in seen:
+                raise StepError(f"request '{s.request_id}' appears twice in one step")
+            seen.add(s.request_id)
+            n = len(s.tokens)
+            if n == 0:
+                raise StepError(f"request '{s.request_id}' brings no tokens")
+            total += n
+            for t in s.tokens:
+                if not (0 <= t < self.vocab_size):
+                    raise StepError(f"request '{s.request_id}': token id {t} is outside the vocabulary "
+                                    f"[0, {self.vocab_size})")
+            s.slot = self.cache.slot(s.request_id)
+            s.start = self.cache.length(s.request_id)
+            if s.start + n > self.max_position:
+                raise StepError(f"request '{s.request_id}' would reach position {s.start + n - 1}, beyond "
+                                f"max_position_embeddings = {self.max_position}")   # model.cpp:1209-1211
+        if self.max_tokens_per_step is not None and total > self.max_tokens_per_step:
+            raise StepError(f"{total} tokens in one step, the limit is {self.max_tokens_per_step}")
+        for s in segments:
+            self.cache.reserve(s.request_id, s.start + len(s.tokens))
+
+    def step(self, segments: list) -> torch.Tensor:
+        """segments: list of ``Segment(request_id, tokens, want)``.  Returns float32 logits
+        [number of wanted places, vocab] in the order of the segments and of their ``want`` lists."""
+        self.prepare(segments)
+        self.cache.sync_tables()
+        ctx = StepContext.build(segments, self.runtime, self.cache)
+        logits = self.model.forward(ctx)
+        for s in segments:
+            self.cache.commit(s.request_id, s.start + len(s.tokens))
+        self._last_ctx = ctx
+        return logits
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel of the last step met a token without a page (costs a device sync)."""
+        if self._last_ctx is not None and self._last_ctx.error_count is not None:
+            bad = int(self._last_ctx.error_count.item())
+            if bad:
+                raise StepError(f"{bad} key/value rows had no page to go to: block table and batch disagree")

@@ -1,0 +1,327 @@
+"""Python side of the hand-written sm_100a kernels: loads the libraries built from ``csrc/`` and
+wraps each entry point in a function that checks its tensors and launches on torch's current stream.
+
+There is no fallback: if a library cannot be built or loaded, or the tensors are not on a CUDA
+device, the call raises.  Matrix products in bfloat16 go to cuBLAS through ``torch.mm`` (the
+reference engine uses cuBLAS for every product, src/ops/kernels/cuda/matmul_kernel.cu:132-154);
+the float32 path uses the repository's own fp32-FMA kernel so that no reduced-precision mode can
+take part.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from ..csrc import build
+
+F32, BF16 = 0, 1
+SPLIT_KEYS = 256          # keys per range of the split decode attention (a multiple of the 64-key tile)
+_LIBS: dict = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _lib(name: str, head_dim: int | None = None) -> ctypes.CDLL:
+    key = (name, head_dim)
+    lib = _LIBS.get(key)
+    if lib is None:
+        path = build.library_path(name, head_dim)
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as exc:
+            raise KernelError(f"cannot load kernel library {path}: {exc}") from exc
+        lib.pi_last_error.restype = ctypes.c_char_p
+        _LIBS[key] = lib
+    return lib
+
+
+def _check(lib, rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed (code {rc}): {lib.pi_last_error().decode(errors='replace')}")
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}")
+
+
+def _p(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels run on a CUDA device only; got a tensor on " + str(t.device))
+
+
+def _need_contig(**tensors) -> None:
+    for name, t in tensors.items():
+        if t is not None and not t.is_contiguous():
+            raise KernelError(f"tensor '{name}' must be contiguous")
+
+
+def preload(head_dims=(), simple_attention: bool = True) -> None:
+    """Build and load what a model needs, so that the first step does not pay for it."""
+    for name in ("elementwise", "gemm_f32", "sampling"):
+        _lib(name)
+    if simple_attention:
+        _lib("attention_simple")
+    for d in head_dims:
+        _lib("attention_mma", d)
+
+
+# ---- embedding --------------------------------------------------------------------------------------
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """tokens int32 [T], table [V, H] (bf16 or fp32) -> fp32 residual [T, H]."""
+    _need_cuda(tokens, table)
+    _need_contig(tokens=tokens, table=table)
+    if tokens.dtype != torch.int32:
+        raise KernelError("token ids must be int32")
+    T, (V, H) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.pi_embed(_p(tokens), _p(table), c_int(_code(table.dtype)), _p(out), c_int(T), c_int(H), c_int(V),
+                             _stream()), "embedding")
+    return out
+
+
+# ---- fused residual add + RMSNorm ---------------------------------------------------------------------
+def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """hidden fp32 [T, H].  Without ``rows``: hidden += delta in place and the norm of every row is
+    returned.  With ``rows`` (int32 [n]): the norm of hidden[rows] + delta[rows]; hidden is not changed."""
+    _need_cuda(hidden, delta, weight, rows)
+    _need_contig(hidden=hidden, delta=delta, weight=weight, rows=rows)
+    if hidden.dtype != torch.float32:
+        raise KernelError("the residual stream must be float32")
+    T, H = hidden.shape
+    if delta is not None and (delta.shape != hidden.shape or delta.dtype != out_dtype):
+        raise KernelError(f"delta must be {tuple(hidden.shape)} of {out_dtype}, got {tuple(delta.shape)} of {delta.dtype}")
+    if weight.shape != (H,):
+        raise KernelError(f"norm weight must have shape ({H},), got {tuple(weight.shape)}")
+    n = T if rows is None else rows.numel()
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("rows must be int32")
+    if out is None:
+        out = torch.empty((n, H), dtype=out_dtype, device=hidden.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.pi_add_rmsnorm(_p(hidden), _p(delta), _p(weight), c_int(_code(weight.dtype)), _p(out),
+                                   c_int(_code(out_dtype)), _p(rows), c_int(n), c_int(H), c_float(eps), _stream()),
+           "add_rmsnorm")
+    return out
+
+
+# ---- SiLU(gate) * up ------------------------------------------------------------------------------------
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """gate_up [T, 2*I] (gate columns first) -> [T, I]."""
+    _need_cuda(gate_up)
+    _need_contig(gate_up=gate_up)
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up must have an even number of columns")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((T, inter), dtype=gate_up.dtype, device=gate_up.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.pi_silu_mul(_p(gate_up), _p(out), c_int(_code(gate_up.dtype)), c_int(T), c_int(inter), _stream()),
+           "silu_mul")
+    return out
+
+
+# ---- rotation tables --------------------------------------------------------------------------------------
+def rope_table(positions: torch.Tensor, divisors: torch.Tensor):
+    """positions int32 [T], divisors float64 [pairs] (theta^(2i/rot)) -> cos, sin fp32 [T, pairs]."""
+    _need_cuda(positions, divisors)
+    _need_contig(positions=positions, divisors=divisors)
+    if positions.dtype != torch.int32 or divisors.dtype != torch.float64:
+        raise KernelError("positions must be int32 and divisors float64")
+    T, pairs = positions.numel(), divisors.numel()
+    cos = torch.empty((T, pairs), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    lib = _lib("elementwise")
+    _check(lib, lib.pi_rope_table(_p(positions), _p(divisors), _p(cos), _p(sin), c_int(T), c_int(pairs), _stream()),
+           "rope_table")
+    return cos, sin
+
+
+# ---- fused per-head norm + rotation + paged key/value write ---------------------------------------------
+def qk_norm_rope_write(qkv: torch.Tensor, q_weight, k_weight, eps: float, cos, sin, adjacent_pairs: bool,
+                       kcache, vcache, block_table, token_slot: torch.Tensor, positions: torch.Tensor,
+                       page_size: int, nq: int, nkv: int, head_dim: int, error_count: torch.Tensor) -> None:
+    """qkv [T, (nq + 2*nkv) * d]: query heads are normalised and rotated in place; key heads are
+    normalised, rotated and written to ``kcache``; value heads are copied to ``vcache`` (both
+    [pages, nkv, page_size, d]).  ``q_weight``/``k_weight`` None: no per-head norm.  ``cos``/``sin``
+    None: no rotation.  ``nkv`` = 0 for a layer that only reads another layer's cache."""
+    _need_cuda(qkv, q_weight, k_weight, cos, sin, kcache, vcache, block_table, token_slot, positions, error_count)
+    _need_contig(qkv=qkv, kcache=kcache, vcache=vcache, block_table=block_table, cos=cos, sin=sin)
+    T, width = qkv.shape
+    if width != (nq + 2 * nkv) * head_dim:
+        raise KernelError(f"qkv has {width} columns, expected (nq + 2 nkv) * d = {(nq + 2 * nkv) * head_dim}")
+    has_norm = q_weight is not None
+    if has_norm and (q_weight.shape != (head_dim,) or (nkv and k_weight.shape != (head_dim,))):
+        raise KernelError("per-head norm weights must have shape (head_dim,)")
+    rot_pairs = 0 if cos is None else cos.shape[1]
+    if cos is not None and (cos.shape != (T, rot_pairs) or sin.shape != cos.shape or cos.dtype != torch.float32):
+        raise KernelError("rotation tables must be float32 [T, pairs]")
+    if nkv:
+        if kcache.dtype != qkv.dtype or vcache.dtype != qkv.dtype or kcache.shape != vcache.shape:
+            raise KernelError("key and value pages must match the activation dtype and each other")
+        if kcache.shape[1:] != (nkv, page_size, head_dim):
+            raise KernelError(f"pages must be [n, {nkv}, {page_size}, {head_dim}], got {tuple(kcache.shape)}")
+    wdtype = q_weight.dtype if has_norm else torch.float32
+    lib = _lib("elementwise")
+    _check(lib, lib.pi_qk_norm_rope_write(
+        _p(qkv), c_int(width), c_int(_code(qkv.dtype)), _p(q_weight), _p(k_weight if nkv else q_weight),
+        c_int(_code(wdtype)), c_float(eps), c_int(1 if has_norm else 0), _p(cos), _p(sin), c_int(rot_pairs),
+        c_int(1 if adjacent_pairs else 0), _p(kcache), _p(vcache), _p(block_table),
+        c_int(block_table.shape[1] if block_table is not None else 0), _p(token_slot), _p(positions),
+        c_int(page_size), c_int(nq), c_int(nkv), c_int(head_dim), c_int(T), _p(error_count), _stream()),
+        "qk_norm_rope_write")
+
+
+# ---- attention ------------------------------------------------------------------------------------------------
+def attention_simple(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, token_slot, positions,
+                     num_tokens: int, nq: int, nkv: int, head_dim: int, page_size: int, window: int | None,
+                     scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Plain paged attention (float32 or bfloat16).  ``q`` holds the query heads of token t at
+    element offset t * q_stride.  Returns [T, nq * d]."""
+    _need_cuda(q, kcache, vcache, block_table, token_slot, positions)
+    _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
+    if out is None:
+        out = torch.empty((num_tokens, nq * head_dim), dtype=q.dtype, device=q.device)
+    lib = _lib("attention_simple")
+    _check(lib, lib.pi_attention_simple(
+        _p(q), c_int(q_stride), _p(kcache), _p(vcache), c_int(_code(q.dtype)), _p(block_table),
+        c_int(block_table.shape[1]), _p(token_slot), _p(positions), _p(out), c_int(num_tokens), c_int(nq), c_int(nkv),
+        c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale), _stream()), "attention_simple")
+    return out
+
+
+def attention_num_splits(pos: int, window: int | None, split_keys: int = SPLIT_KEYS) -> int:
+    """Key ranges a decoding request whose newest token sits at ``pos`` is cut into (depends on its own
+    length and the window only, never on the batch)."""
+    w = window or 0
+    lo = max(0, pos - w + 1) if w > 0 else 0
+    lo_al = (lo // 64) * 64
+    return (pos + 1 - lo_al + split_keys - 1) // split_keys
+
+
+def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len,
+                  token_seg, num_tokens: int, num_segments: int, max_seg_len: int, has_prompt: bool, has_decode: bool,
+                  max_splits: int, part_acc, part_ml, nq: int, nkv: int, head_dim: int, page_size: int,
+                  window: int | None, scale: float, out: torch.Tensor | None = None,
+                  split_keys: int = SPLIT_KEYS) -> torch.Tensor:
+    """Tensor-core paged attention for bfloat16 over request segments (see csrc/attention_mma.cu)."""
+    _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml)
+    _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention kernel takes bfloat16 only")
+    if out is None:
+        out = torch.empty((num_tokens, nq * head_dim), dtype=q.dtype, device=q.device)
+    if has_decode and max_splits > 1:
+        need = num_tokens * nq * max_splits
+        if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:
+            raise KernelError("scratch for the split decode attention is missing or too small")
+    lib = _lib("attention_mma", head_dim)
+    _check(lib, lib.pi_attention_mma(
+        _p(q), c_int(q_stride), _p(kcache), _p(vcache), _p(block_table), c_int(block_table.shape[1]), _p(seg_off),
+        _p(seg_slot), _p(seg_start), _p(seg_len), _p(token_seg), _p(out), _p(part_acc), _p(part_ml), c_int(max_splits),
+        c_int(split_keys), c_int(num_tokens), c_int(num_segments), c_int(max_seg_len), c_int(1 if has_prompt else 0),
+        c_int(1 if has_decode else 0), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale),
+        _stream()), "attention_mma")
+    return out
+
+
+# ---- matrix products -----------------------------------------------------------------------------------------------
+def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x fp32 [M, K], weight fp32 [N, K] -> fp32 [M, N] with fp32 FMA in a fixed k order."""
+    _need_cuda(x, weight)
+    if x.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise KernelError("gemm_f32 takes float32 operands")
+    if x.stride(-1) != 1 or weight.stride(-1) != 1:
+        raise KernelError("gemm_f32 needs unit stride along k")
+    M, K = x.shape
+    N, K2 = weight.shape
+    if K != K2:
+        raise KernelError(f"inner sizes differ: {K} vs {K2}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    lib = _lib("gemm_f32")
+    _check(lib, lib.pi_gemm_f32_nt(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
+                                   c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), _stream()), "gemm_f32")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y = x W^T with W [out, in] (src/layer/linear.cpp:213).  A bfloat16 weight runs on cuBLAS with
+    32-bit accumulation; a float32 weight runs on the fp32-FMA kernel, whatever the activation dtype."""
+    _need_cuda(x, weight)
+    out_dtype = out_dtype or x.dtype
+    if weight.dtype == torch.float32:
+        y = gemm_f32(x if x.dtype == torch.float32 else x.float(), weight)
+        return y if out_dtype == torch.float32 else y.to(out_dtype)
+    if weight.dtype != torch.bfloat16:
+        raise KernelError(f"weights must be bfloat16 or float32, not {weight.dtype}")
+    xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    if out_dtype == torch.bfloat16:
+        return torch.mm(xb, weight.t())
+    return torch.mm(xb, weight.t(), out_dtype=torch.float32)
+
+
+# ---- sampling ---------------------------------------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """logits fp32 [n, V] -> int32 [n]; the lowest index wins ties."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or logits.stride(-1) != 1:
+        raise KernelError("logits must be float32 with unit stride")
+    n, V = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    lib = _lib("sampling")
+    _check(lib, lib.pi_argmax(_p(logits), c_int(logits.stride(0)), c_int(n), c_int(V), _p(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seeds: torch.Tensor, counters: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-row temperature / top-k / top-p sampling; temperature <= 0 means greedy for that row.
+    seeds and counters are int64 (read as unsigned); the uniform draw depends on them only."""
+    _need_cuda(logits, temperature, top_k, top_p, seeds, counters)
+    n, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(-1) != 1:
+        raise KernelError("logits must be float32 with unit stride")
+    if (temperature.dtype != torch.float32 or top_p.dtype != torch.float32 or top_k.dtype != torch.int32
+            or seeds.dtype != torch.int64 or counters.dtype != torch.int64):
+        raise KernelError("sampling parameters: temperature/top_p float32, top_k int32, seeds/counters int64")
+    for name, t in (("temperature", temperature), ("top_k", top_k), ("top_p", top_p), ("seeds", seeds), ("counters", counters)):
+        if t.numel() != n or not t.is_contiguous():
+            raise KernelError(f"sampling parameter '{name}' must hold one contiguous value per row")
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    lib = _lib("sampling")
+    _check(lib, lib.pi_sample(_p(logits), c_int(logits.stride(0)), c_int(n), c_int(V), _p(temperature), _p(top_k),
+                              _p(top_p), _p(seeds), _p(counters), _p(out), _stream()), "sample")
+    return out
+
+
+def logit_edit(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, values: torch.Tensor, set_value: bool) -> None:
+    """logits[rows[i], tokens[i]] += values[i] (or = values[i]); pairs must be distinct."""
+    _need_cuda(logits, rows, tokens, values)
+    n = rows.numel()
+    lib = _lib("sampling")
+    _check(lib, lib.pi_logit_edit(_p(logits), c_int(logits.stride(0)), c_int(logits.shape[1]), _p(rows), _p(tokens),
+                                  _p(values), c_int(n), c_int(1 if set_value else 0), _stream()), "logit_edit")
