@@ -1,0 +1,322 @@
+"""Each kernel alone against a plain reference, at sizes other than the engine tests use."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from gpu_util import PagedKV, dense_attention, need_gpu, segments_to_device
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from pulse_infer_b200 import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(dtype):
+    dev, ops = need_gpu(), _ops()
+    table = torch.randn(1000, 202).to(dtype)
+    tokens = torch.tensor([0, 999, 5, 5, 123, 1000, -1], dtype=torch.int32)
+    out = ops.embed(tokens.to(dev), table.to(dev)).cpu()
+    want = torch.from_numpy(plain_model.embedding(table.float().numpy(), tokens.tolist()))
+    assert out.dtype == torch.float32 and torch.equal(out, want)
+
+
+@pytest.mark.parametrize("hidden", [4096, 202, 77])
+@pytest.mark.parametrize("act,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+def test_add_rmsnorm(hidden, act, wdt):
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(hidden)
+    h = torch.randn(9, hidden, generator=g) * 3
+    delta = torch.randn(9, hidden, generator=g).to(act)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(wdt)
+    eps = 1e-5
+    hd = h.clone().to(dev)
+    x = ops.add_rmsnorm(hd, delta.to(dev), w.to(dev), eps, act).cpu()
+    s = h.double() + delta.double()
+    want = plain_model.rms_norm(s.numpy(), w.double().numpy(), eps)
+    assert torch.allclose(hd.cpu().double(), s, atol=1e-6, rtol=1e-6)          # the residual is 32-bit
+    tol = 1e-5 if act == torch.float32 else 2 ** -8
+    assert np.abs(x.double().numpy() - want).max() <= tol * np.abs(want).max()
+    # without a delta, and gathered rows that leave the residual untouched
+    x0 = ops.add_rmsnorm(h.clone().to(dev), None, w.to(dev), eps, act).cpu()
+    assert np.abs(x0.double().numpy() - plain_model.rms_norm(h.double().numpy(), w.double().numpy(), eps)).max() <= tol * 4
+    rows = torch.tensor([7, 0, 7, 3], dtype=torch.int32)
+    hd2 = h.clone().to(dev)
+    xr = ops.add_rmsnorm(hd2, delta.to(dev), w.to(dev), eps, act, rows=rows.to(dev)).cpu()
+    assert torch.equal(hd2.cpu(), h)
+    assert np.abs(xr.double().numpy() - want[rows.long().numpy()]).max() <= tol * np.abs(want).max()
+
+
+@pytest.mark.parametrize("inter", [12288, 222, 7])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(inter, dtype):
+    dev, ops = need_gpu(), _ops()
+    gu = (torch.randn(5, 2 * inter, generator=torch.Generator().manual_seed(1)) * 4).to(dtype)
+    out = ops.silu_mul(gu.to(dev)).cpu().double().numpy()
+    g, u = gu[:, :inter].double().numpy(), gu[:, inter:].double().numpy()
+    want = plain_model.silu(g) * u
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert np.abs(out - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+def test_rope_table_large_positions():
+    dev, ops = need_gpu(), _ops()
+    pos = torch.tensor([0, 1, 17, 4095, 131071], dtype=torch.int32)
+    rot, theta = 96, 1e6
+    div = torch.tensor([theta ** (2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64)
+    cos, sin = ops.rope_table(pos.to(dev), div.to(dev))
+    ang = pos.double()[:, None] / div[None, :]
+    assert (cos.cpu().double() - torch.cos(ang)).abs().max() < 1e-7
+    assert (sin.cpu().double() - torch.sin(ang)).abs().max() < 1e-7
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,rot,adjacent,page", [(6, 2, 48, 48, True, 8), (8, 1, 32, 16, False, 16),
+                                                        (5, 5, 80, 80, False, 4), (4, 2, 256, 256, True, 16)])
+def test_qk_norm_rope_write(dtype, nq, nkv, d, rot, adjacent, page):
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(nq * d)
+    segs = [(1, 13, 9), (0, 0, 5), (2, 40, 1)]            # (slot, start, length)
+    meta = segments_to_device(segs, dev)
+    T = meta["T"]
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    qw = (1 + 0.2 * torch.randn(d, generator=g)).to(dtype)
+    kw = (1 + 0.2 * torch.randn(d, generator=g)).to(dtype)
+    eps, theta = 1e-5, 10000.0
+    pages = 24
+    table = torch.full((3, 8), -1, dtype=torch.int32)
+    perm = torch.randperm(pages, generator=g).tolist()
+    for slot, start, n in segs:
+        for i in range((start + n + page - 1) // page):
+            table[slot, i] = perm.pop()
+    kc = torch.zeros(pages, nkv, page, d, dtype=dtype, device=dev)
+    vc = torch.zeros_like(kc)
+    div = torch.tensor([theta ** (2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64, device=dev)
+    cos, sin = ops.rope_table(meta["positions"], div)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    dq = qkv.clone().to(dev)
+    ops.qk_norm_rope_write(dq, qw.to(dev), kw.to(dev), eps, cos, sin, adjacent, kc, vc, table.to(dev),
+                           meta["token_slot"], meta["positions"], page, nq, nkv, d, err)
+    assert int(err.item()) == 0
+    x = qkv.double().numpy().reshape(T, nq + 2 * nkv, d)
+    positions = meta["positions"].cpu().numpy()
+    pairing = "adjacent" if adjacent else "half"
+    q_want = plain_model.rope(plain_model.rms_norm(x[:, :nq], qw.double().numpy(), eps), positions, theta, rot, pairing)
+    k_want = plain_model.rope(plain_model.rms_norm(x[:, nq:nq + nkv], kw.double().numpy(), eps), positions, theta, rot, pairing)
+    v_want = x[:, nq + nkv:]
+    tol = 2e-6 if dtype == torch.float32 else 2 ** -7
+    got = dq.cpu().double().numpy().reshape(T, nq + 2 * nkv, d)
+    assert np.abs(got[:, :nq] - q_want).max() <= tol * np.abs(q_want).max()
+    assert np.array_equal(got[:, nq:], x[:, nq:])                      # key/value columns are left alone
+    kcc, vcc = kc.cpu().double().numpy(), vc.cpu().double().numpy()
+    tslot = meta["token_slot"].cpu().numpy()
+    for t in range(T):
+        p = int(table[tslot[t], positions[t] // page]); s = positions[t] % page
+        assert np.abs(kcc[p, :, s] - k_want[t]).max() <= tol * np.abs(k_want).max()
+        assert np.array_equal(vcc[p, :, s], v_want[t])
+    # nothing else was written
+    written = np.zeros((pages, page), dtype=bool)
+    for t in range(T):
+        written[int(table[tslot[t], positions[t] // page]), positions[t] % page] = True
+    assert not kcc.transpose(0, 2, 1, 3)[~written].any() and not vcc.transpose(0, 2, 1, 3)[~written].any()
+    # a token whose page is missing is counted, not written
+    bad = table.clone(); bad[2, 40 // page] = -1
+    ops.qk_norm_rope_write(qkv.clone().to(dev), qw.to(dev), kw.to(dev), eps, cos, sin, adjacent, kc, vc, bad.to(dev),
+                           meta["token_slot"], meta["positions"], page, nq, nkv, d, err)
+    assert int(err.item()) == 2 * nkv
+
+
+def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengths, seed=0, spike=None):
+    """segs: (slot, start, n) with start + n <= lengths[slot]; queries random; returns max error / scale."""
+    kv = PagedKV(lengths, nkv, d, page, dtype, dev, seed=seed)
+    meta = segments_to_device(segs, dev)
+    T = meta["T"]
+    g = torch.Generator().manual_seed(seed + 1)
+    q = torch.randn(T, nq, d, generator=g).to(dtype)
+    if spike is not None:
+        slot, key_pos, head = spike
+        kvh = head // (nq // nkv)
+        # the spiked key is a large multiple of the LAST query of that slot's segment, head `head`
+        t_last = [o + n - 1 for (s, st, n), o in zip(segs, meta["seg_off"].tolist()) if s == slot][0]
+        big = (q[t_last, head].double() * 6.0).to(dtype)
+        page_id = int(kv.table[slot, key_pos // page])
+        kv.kcache[page_id, kvh, key_pos % page] = big.to(dev)
+        kv.k_dense[slot][key_pos, kvh] = big.double()
+    scale = 1.0 / math.sqrt(d)
+    qflat = q.reshape(T, nq * d).contiguous().to(dev)
+    if impl == "simple":
+        out = ops.attention_simple(qflat, nq * d, kv.kcache, kv.vcache, kv.table_dev, meta["token_slot"],
+                                   meta["positions"], T, nq, nkv, d, page, window, scale)
+    else:
+        lens = [n for _, _, n in segs]
+        dec_pos = max([st for _, st, n in segs if n == 1], default=0)
+        splits = ops.attention_num_splits(dec_pos, window) if any(n == 1 for n in lens) else 1
+        acc = torch.empty(T * nq * splits * d, dtype=torch.float32, device=dev)
+        ml = torch.empty(T * nq * splits * 2, dtype=torch.float32, device=dev)
+        out = ops.attention_mma(qflat, nq * d, kv.kcache, kv.vcache, kv.table_dev, meta["seg_off"], meta["seg_slot"],
+                                meta["seg_start"], meta["seg_len"], meta["token_seg"], T, len(segs), max(lens),
+                                any(n > 1 for n in lens), any(n == 1 for n in lens), splits, acc, ml, nq, nkv, d, page,
+                                window, scale)
+    out = out.cpu().double().reshape(T, nq, d)
+    worst = 0.0
+    for (slot, start, n), off in zip(segs, meta["seg_off"].tolist()):
+        want = dense_attention(q[off:off + n].double(), kv.k_dense[slot], kv.v_dense[slot],
+                               list(range(start, start + n)), window, scale)
+        worst = max(worst, float((out[off:off + n] - want).abs().max()))
+    return worst
+
+
+ATTN_SHAPES = [  # nq, nkv, d, page
+    (4, 2, 16, 8), (8, 1, 32, 16), (6, 2, 48, 16), (3, 3, 64, 4), (32, 8, 128, 16), (5, 1, 80, 8), (2, 1, 256, 16),
+    (40, 2, 64, 16)]
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention_simple_float32(nq, nkv, d, page, window):
+    dev, ops = need_gpu(), _ops()
+    lengths = [150, 70, 301, 9]
+    segs = [(0, 100, 50), (1, 69, 1), (2, 0, 301), (3, 7, 2)]
+    err = _attention_case(ops, dev, torch.float32, "simple", nq, nkv, d, page, window, segs, lengths)
+    assert err < 2e-5
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [s for s in ATTN_SHAPES if s[2] % 16 == 0])
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("impl", ["mma", "simple"])
+def test_attention_bfloat16_prompt_and_decode(nq, nkv, d, page, window, impl):
+    dev, ops = need_gpu(), _ops()
+    lengths = [150, 70, 301, 9, 1000]
+    # portions at odd offsets, single tokens at page edges (63|64, 255|256), one long decode that is split
+    segs = [(0, 100, 50), (1, 69, 1), (2, 0, 301), (3, 7, 2), (4, 999, 1)]
+    err = _attention_case(ops, dev, torch.bfloat16, impl, nq, nkv, d, page, window, segs, lengths)
+    assert err < 0.03      # bfloat16 probabilities and outputs: about 2^-7 of values of order one
+
+
+@pytest.mark.parametrize("ctx", [1, 2, 15, 16, 17, 63, 64, 65, 255, 256, 257, 511, 512, 513, 1300])
+def test_attention_mma_decode_every_edge(ctx):
+    dev, ops = need_gpu(), _ops()
+    err = _attention_case(ops, dev, torch.bfloat16, "mma", 8, 2, 64, 16, None, [(0, ctx - 1, 1)], [ctx], seed=ctx)
+    assert err < 0.03
+
+
+@pytest.mark.parametrize("impl,dtype", [("mma", torch.bfloat16), ("simple", torch.bfloat16), ("simple", torch.float32)])
+@pytest.mark.parametrize("key_pos", [0, 15, 16, 300, 511, 512, 700])
+def test_attention_finds_one_far_key(impl, dtype, key_pos):
+    """One key among hundreds carries nearly all the weight: the output must be that key's value."""
+    dev, ops = need_gpu(), _ops()
+    nq, nkv, d, page = 8, 2, 64, 16
+    lengths = [800]
+    for segs in ([(0, 799, 1)], [(0, 760, 40)]):
+        kv_err = _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, None, segs, lengths, seed=3,
+                                 spike=(0, key_pos, 5))
+        assert kv_err < (0.03 if dtype == torch.bfloat16 else 1e-4)
+
+
+def test_attention_window_edge_exact():
+    """Keys just outside the window hold huge values; any leak shows."""
+    dev, ops = need_gpu(), _ops()
+    for impl, dtype in (("mma", torch.bfloat16), ("simple", torch.float32)):
+        for window in (1, 16, 17, 64, 65):
+            err = _attention_case(ops, dev, dtype, impl, 4, 2, 32, 16, window, [(0, 190, 10), (1, 99, 1)], [200, 100])
+            assert err < (0.03 if dtype == torch.bfloat16 else 2e-5)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 515, 96), (33, 515, 100), (64, 64, 16), (130, 77, 1000), (7, 4096, 4096)])
+def test_gemm_f32_true_32bit(M, N, K):
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(M + N)
+    x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    out = ops.gemm_f32(x.to(dev), w.to(dev)).cpu()
+    want = x.double() @ w.double().t()
+    bound = 2e-7 * K * float((x.abs().double() @ w.abs().double().t()).max())     # k roundings of eps/2
+    assert float((out.double() - want).abs().max()) <= bound
+    # tf32 would be off by about 1e-3 relative; make sure we are nowhere near
+    assert float((out.double() - want).abs().max()) <= 1e-5 * float(want.abs().max()) * math.sqrt(K)
+    # a row's result does not depend on the rows around it
+    one = ops.gemm_f32(x[M // 2:M // 2 + 1].contiguous().to(dev), w.to(dev)).cpu()
+    assert torch.equal(one[0], out[M // 2])
+
+
+def test_linear_bfloat16_and_mixed():
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(17, 200, generator=g).to(torch.bfloat16)
+    w = torch.randn(515, 200, generator=g).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    y32 = ops.linear(x.to(dev), w.to(dev), torch.float32).cpu()
+    assert y32.dtype == torch.float32 and float((y32.double() - want).abs().max()) < 1e-3
+    yb = ops.linear(x.to(dev), w.to(dev), torch.bfloat16).cpu()
+    assert yb.dtype == torch.bfloat16 and float((yb.double() - want).abs().max()) < 0.02 * float(want.abs().max())
+    yf = ops.linear(x.to(dev), w.float().to(dev), torch.bfloat16).cpu()      # a weight kept in 32-bit
+    assert float((yf.double() - want).abs().max()) < 0.02 * float(want.abs().max())
+
+
+def test_argmax_lowest_index_wins():
+    dev, ops = need_gpu(), _ops()
+    logits = torch.randn(6, 151936, generator=torch.Generator().manual_seed(0))
+    logits[0, 777] = 50.0; logits[0, 90000] = 50.0
+    logits[1, 151935] = 60.0
+    logits[2, 0] = 60.0
+    logits[3, 5] = float("nan"); logits[3, 6] = 70.0
+    got = ops.argmax(logits.to(dev)).cpu().tolist()
+    assert got[:4] == [777, 151935, 0, 6]
+    assert got[4:] == [plain_model.greedy(logits[i].numpy()) for i in (4, 5)]
+    small = torch.tensor([[1.0, 3.0, 3.0, 2.0, 3.0]] * 2)
+    assert ops.argmax(small.to(dev)).cpu().tolist() == [1, 1]
+
+
+def _sample(ops, dev, logits, temp, k, p, seed, counters):
+    n = logits.shape[0]
+    f = lambda v, dt: torch.full((n,), v, dtype=dt, device=dev)  # noqa: E731
+    return ops.sample(logits.to(dev), f(temp, torch.float32), f(k, torch.int32), f(p, torch.float32),
+                      f(seed, torch.int64), torch.tensor(counters, dtype=torch.int64, device=dev)).cpu().tolist()
+
+
+@pytest.mark.parametrize("vocab", [515, 40000])
+@pytest.mark.parametrize("temp,k,p", [(0.8, 0, 0.0), (1.3, 20, 0.0), (0.6, 20, 0.95), (1.0, 0, 0.5), (0.7, 1, 0.0)])
+def test_sampling_matches_plain_sampler(vocab, temp, k, p):
+    dev, ops = need_gpu(), _ops()
+    base = torch.randn(vocab, generator=torch.Generator().manual_seed(vocab)) * 2.5
+    base[3] = base[11] = base.max() + 0.5                      # a tie at the top
+    n = 64
+    logits = base.repeat(n, 1).contiguous()
+    counters = list(range(n))
+    got = _sample(ops, dev, logits, temp, k, p, 1234, counters)
+    order, _ = plain_model.kept_set(base.double().numpy(), temp, k, p)
+    assert set(got) <= set(order)
+    # same uniform numbers, same walk: tokens agree except where rounding of the cumulative sums decides
+    want = [plain_model.sample(base.double().numpy(), temp, k, p, 1234, c) for c in counters]
+    agree = sum(int(a == b) for a, b in zip(got, want))
+    assert agree >= n - 2
+    assert _sample(ops, dev, logits[:4], 0.0, k, p, 1, [0, 1, 2, 3]) == [3, 3, 3, 3]   # temperature 0 is greedy
+
+
+def test_sampling_distribution():
+    dev, ops = need_gpu(), _ops()
+    base = torch.tensor([2.0, 1.0, 0.0, -1.0, 1.5, -30.0])
+    n = 4000
+    got = _sample(ops, dev, base.repeat(n, 1).contiguous(), 1.0, 0, 0.0, 99, list(range(n)))
+    freq = np.bincount(got, minlength=6) / n
+    prob = torch.softmax(base.double(), 0).numpy()
+    assert np.abs(freq - prob).max() < 0.03
+    # the draw depends on (seed, counter) only, not on the row's place in the batch
+    again = _sample(ops, dev, base.repeat(5, 1).contiguous(), 1.0, 0, 0.0, 99, [7, 7, 3, 7, 3])
+    assert again[0] == again[1] == again[3] == got[7] and again[2] == again[4] == got[3]
+
+
+def test_logit_edit():
+    dev, ops = need_gpu(), _ops()
+    logits = torch.zeros(3, 100, device=dev)
+    mk = lambda v, dt: torch.tensor(v, dtype=dt, device=dev)  # noqa: E731
+    ops.logit_edit(logits, mk([0, 2, 2], torch.int32), mk([5, 7, 99], torch.int32), mk([-1.5, -1.5, -1.5], torch.float32), False)
+    ops.logit_edit(logits, mk([1], torch.int32), mk([0], torch.int32), mk([float("-inf")], torch.float32), True)
+    out = logits.cpu()
+    assert out[0, 5] == -1.5 and out[2, 7] == -1.5 and out[2, 99] == -1.5 and out[1, 0] == float("-inf")
+    assert out.isfinite().sum() == 299 and (out == 0).sum() == 296
