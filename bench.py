@@ -1,0 +1,308 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens per second of a Qwen3-8B-shaped model in bfloat16
+with random weights (batch 8, context up to 4096), plus a 2,048-token prefill, decode at batch 1 and 64,
+the same decode measured end to end through the Python entry point, and roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  Prompts are 2,048 seeded uniform-random token ids per
+request; the requests are decoded (untimed) until W + K steps before the context length 4096, then W
+warm-up steps and exactly K timed steps follow, bracketed by CUDA events.  Every step reads all weights
+(15 GB), far more than the 126 MB L2, so no flush is needed between steps.  One JSON line is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# layer sizes of BASELINE.json configs[2] (Qwen3-8B shape)
+SHAPE = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+             intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+             max_position_embeddings=40960)
+FULL_LAYERS = 36
+CONTEXT = 4096
+PROMPT = 2048
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks, source = dict(FALLBACK_PEAKS), "fallback"
+    if os.path.isfile(path):
+        try:
+            with open(path) as fh:
+                obj = json.load(fh)
+            for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if isinstance(obj.get(key), (int, float)):
+                    peaks[key] = float(obj[key])
+            source = "measured"
+        except (OSError, ValueError):
+            pass
+    return peaks, source
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.monotonic(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return None
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [l for t, l in self.samples if t0 <= t <= t1] or [l for _, l in self.samples[-3:]]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in rows:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_config(layers: int):
+    from pulse_infer_b200.config import Qwen3Config
+    return Qwen3Config(architecture="Qwen3ForCausalLM", torch_dtype="bfloat16", eos_token_ids=(), **{**SHAPE, "num_hidden_layers": layers})
+
+
+def weight_bytes_per_step(cfg) -> int:
+    """Bytes of weights a decode step reads once: every layer's matrices and norms, the final norm, the head."""
+    H, Q, KV, I, V, L = cfg.hidden_size, cfg.q_size, cfg.kv_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    per_layer = H * (Q + 2 * KV) + Q * H + 3 * H * I + 2 * H + 2 * cfg.head_dim
+    return 2 * (L * per_layer + H + V * H)
+
+
+def kv_bytes(cfg, batch: int, ctx: float) -> float:
+    return batch * ctx * 2 * cfg.num_hidden_layers * cfg.kv_size * 2
+
+
+def prefill_flops(cfg, T: int) -> float:
+    H, Q, KV, I, V, L = cfg.hidden_size, cfg.q_size, cfg.kv_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    linear = 2.0 * T * L * (H * (Q + 2 * KV) + Q * H + 3 * H * I) + 2.0 * H * V
+    attention = 4.0 * cfg.num_attention_heads * cfg.head_dim * (T * (T + 1) / 2) * L
+    return linear + attention
+
+
+def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: bool):
+    """``steps`` timed decode steps of ``batch`` requests whose prompts were 2,048 random ids, ending at
+    context 4096.  through_api=False: the step function with device-side argmax and pre-drawn input
+    tokens (no host round trip between steps).  through_api=True: Engine.step() - every step takes host
+    tokens in (pinned metadata buffer, one copy) and brings the sampled tokens back to the host.
+    Returns (ms per step, launches of own kernels, mean context, h2d bytes, d2h bytes per step)."""
+    import torch
+    from pulse_infer_b200 import ops
+    from pulse_infer_b200.engine import Segment
+    from pulse_infer_b200.engine.context import StepContext
+    vocab = engine.config.vocab_size
+    runner = engine.runner
+    prompts = [[int(t) for t in rng.randint(0, vocab, size=PROMPT)] for _ in range(batch)]
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h2d = StepContext.layout(batch, batch, batch)["_total"][1] * 4
+    if through_api:
+        ids = [engine.add_request(p, CONTEXT, ignore_eos=True) for p in prompts]
+        reqs = [engine.get_request(i) for i in ids]
+        # requests finish their prompts in different steps, so they stay a few tokens apart
+        while any(r.is_prefill() for r in reqs):
+            engine.step()
+        lead = max(r.total_input_tokens() for r in reqs)
+        while lead < CONTEXT - (steps + warmup):
+            engine.step()
+            lead += 1
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        ctx_before = sum(r.total_input_tokens() for r in reqs) / batch
+        before = ops.kernels.LAUNCHES
+        ev0.record()
+        for _ in range(steps):
+            engine.step()
+        ev1.record()
+        torch.cuda.synchronize()
+        mean_ctx = ctx_before + steps / 2.0
+        d2h = batch * 4
+        for i in ids:
+            engine.abort(i)
+    else:
+        rids = [("bench", j) for j in range(batch)]
+        for rid, p in zip(rids, prompts):
+            runner.open(rid)
+            runner.step([Segment(rid, p, [])])                       # one prompt per step
+        advance = CONTEXT - (steps + warmup) - PROMPT
+        draws = rng.randint(0, vocab, size=(advance + steps + warmup, batch))
+        out = torch.empty(batch, dtype=torch.int32, device=runner.runtime.device)
+
+        def one(k):
+            logits = runner.step([Segment(rid, [int(draws[k, j])], [0]) for j, rid in enumerate(rids)])
+            ops.argmax(logits, out)
+        for k in range(advance + warmup):
+            one(k)
+        torch.cuda.synchronize()
+        before = ops.kernels.LAUNCHES
+        ev0.record()
+        for k in range(advance + warmup, advance + warmup + steps):
+            one(k)
+        ev1.record()
+        torch.cuda.synchronize()
+        assert all(runner.cache.length(rid) == CONTEXT for rid in rids)
+        mean_ctx = CONTEXT - steps / 2.0
+        d2h = 0
+        for rid in rids:
+            runner.close(rid)
+    launches = ops.kernels.LAUNCHES - before
+    ms = ev0.elapsed_time(ev1) / steps
+    return ms, launches, mean_ctx, h2d, d2h
+
+
+def timed_prefill(engine, rng, repeats: int = 3):
+    import torch
+    from pulse_infer_b200.engine import Segment
+    runner = engine.runner
+    tokens = [int(t) for t in rng.randint(0, engine.config.vocab_size, size=PROMPT)]
+    times = []
+    for i in range(repeats + 1):
+        runner.open(("prefill", i))
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        runner.step([Segment(("prefill", i), tokens, [PROMPT - 1])])
+        ev1.record()
+        torch.cuda.synchronize()
+        runner.close(("prefill", i))
+        if i > 0:                       # the first run warms up
+            times.append(ev0.elapsed_time(ev1))
+    return statistics.median(times)
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+    from pulse_infer_b200 import Engine
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    peaks, peak_source = load_peaks()
+    layers = args.layers or FULL_LAYERS
+    cfg = make_config(layers)
+    rng = np.random.RandomState(0)
+    batches = sorted({1, 8, 64} | {args.batch})
+    max_batch = max(batches)
+    t_build = time.time()
+    engine = Engine(None, config=cfg, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=max_batch * (CONTEXT + 256),
+                    max_batch_size=max_batch, chunk_size=PROMPT, max_tokens_per_step=PROMPT + max_batch,
+                    max_tokens_per_request=CONTEXT + 256, use_cuda_graphs=True)
+    build_s = time.time() - t_build
+    wbytes = weight_bytes_per_step(cfg)
+
+    prefill_ms = timed_prefill(engine, rng)
+    pf = prefill_flops(cfg, PROMPT)
+
+    points = {}
+    for b in batches:
+        if b == args.batch:
+            continue
+        ms, _, _, _, _ = timed_decode(engine, b, min(args.steps, 32), args.warmup, rng, through_api=False)
+        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+
+    clocks = ClockSampler()
+    clocks.start()
+    time.sleep(0.3)
+    t0 = time.monotonic()
+    ms, launches, mean_ctx, h2d, _ = timed_decode(engine, args.batch, args.steps, args.warmup, rng, through_api=False)
+    t1 = time.monotonic()
+    clock_info = clocks.stop(t0, t1)
+    points[f"decode_b{args.batch}"] = round(args.batch * 1000.0 / ms, 1)
+    e2e_ms, _, _, h2d_e, d2h_e = timed_decode(engine, args.batch, args.steps, args.warmup, rng, through_api=True)
+
+    value = args.batch * 1000.0 / ms
+    step_bytes = wbytes + kv_bytes(cfg, args.batch, mean_ctx)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    return {
+        "metric": "decode tok/s (Qwen3-8B shape, bf16, batch 8, context to 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, seeded random weights",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": FULL_LAYERS, "hidden": cfg.hidden_size,
+                   "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT, "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (every step reads 15 GB of weights)", "cuda_graphs": True,
+                   "peaks": peak_source},
+        "clocks": clock_info,
+        "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d_e, "d2h_bytes_per_step": d2h_e},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PROMPT * 1000.0 / prefill_ms, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                    "frac": round(pf / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "build_s": round(build_s, 1),
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the 36 of the shape (named in config)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a C++/CMake project without setup.py or "
+                          "pyproject.toml: 'pip install --no-index ... /root/reference' answers 'not installable', and its "
+                          "CMake build fetches spdlog/json/googletest from the network"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, only --gpus 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    result = run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

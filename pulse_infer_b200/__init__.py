@@ -7,3 +7,14 @@ state slots), ``engine`` (step function, scheduler, replay), ``sampling``, ``ops
 kernels and their Python entry points).
 """
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # lazy: importing the package must not need torch.cuda or nvcc
+    if name == "Engine":
+        from .api import Engine
+        return Engine
+    if name == "SamplingParams":
+        from .sampling import SamplingParams
+        return SamplingParams
+    raise AttributeError(name)

@@ -1,0 +1,77 @@
+"""The Python entry point: ``Engine`` wraps configuration, weights, cache, step function, scheduler
+and sampler behind the calls the reference's batching engine offers
+(``include/pulse/scheduler/continuous_batch_engine.hpp:14-35``): ``add_request``,
+``run_until_complete``, ``get_result``, ``get_request``, ``get_stats`` - plus ``generate`` for the common
+case.  Prompts and results are lists of token ids.
+
+    from pulse_infer_b200 import Engine
+    engine = Engine("/path/to/model", dtype="bfloat16", max_batch_size=8)
+    outputs = engine.generate([[1, 2, 3], [4, 5]], max_new_tokens=32)
+"""
+from __future__ import annotations
+
+from .engine.builder import build_runner
+from .engine.engine import ContinuousBatchEngine
+from .sampling import Sampler, SamplingParams
+
+
+class Engine:
+    def __init__(self, model: str | None = None, *, config=None, seed: int | None = None, dtype: str = "bfloat16",
+                 device: str = "cuda:0", page_size: int = 16, num_pages: int | None = None,
+                 max_tokens: int | None = None, max_batch_size: int = 8, chunk_size: int = 256,
+                 max_tokens_per_step: int | None = None, max_tokens_per_request: int | None = None,
+                 use_cuda_graphs: bool = True, attention_impl: str = "auto", rope_pairing: str | None = None):
+        """``model``: folder with config.json and safetensors; or ``config`` + ``seed`` for random weights.
+        The page pool is ``num_pages`` pages of ``page_size`` tokens, or enough for ``max_tokens`` tokens
+        (default: ``max_batch_size`` requests of the model's longest context, capped at 1M tokens)."""
+        spec_options = {} if rope_pairing is None else {"rope_pairing": rope_pairing}
+        if num_pages is None and max_tokens is None:
+            from .config.registry import load_config
+            cfg = config if model is None else load_config(model)
+            max_tokens = min(max_batch_size * cfg.max_position_embeddings, 1 << 20)
+        self.runner = build_runner(model, config=config, seed=seed, dtype=dtype, device=device, page_size=page_size,
+                                   num_pages=num_pages, max_tokens=max_tokens, max_requests=max(max_batch_size, 1),
+                                   max_tokens_per_request=max_tokens_per_request,
+                                   max_tokens_per_step=None, attention_impl=attention_impl,
+                                   use_cuda_graphs=use_cuda_graphs, **spec_options)
+        self.config = self.runner.config
+        self.sampler = Sampler(self.runner.runtime.device)
+        self.engine = ContinuousBatchEngine(self.runner, self.sampler, getattr(self.config, "eos_token_ids", ()),
+                                            max_batch_size=max_batch_size, chunk_size=chunk_size,
+                                            max_tokens_per_step=max_tokens_per_step)
+
+    # ---- the reference engine's calls ------------------------------------------------------------------
+    def add_request(self, prompt_tokens, max_new_tokens: int = 32, *, temperature: float = 0.0, top_k: int = 0,
+                    top_p: float = 0.0, presence_penalty: float = 0.0, banned_tokens=(), seed: int = 0,
+                    ignore_eos: bool = False) -> int:
+        params = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p, presence_penalty=presence_penalty,
+                                banned_tokens=tuple(banned_tokens), seed=seed)
+        return self.engine.add_request(list(prompt_tokens), max_new_tokens, params, ignore_eos)
+
+    def step(self) -> list:
+        return self.engine.step()
+
+    def has_work(self) -> bool:
+        return self.engine.has_work()
+
+    def run_until_complete(self, on_step=None) -> None:
+        self.engine.run_until_complete(on_step)
+
+    def get_result(self, request_id: int) -> list:
+        return self.engine.get_result(request_id)
+
+    def get_request(self, request_id: int):
+        return self.engine.get_request(request_id)
+
+    def get_stats(self):
+        return self.engine.get_stats()
+
+    def abort(self, request_id: int) -> None:
+        self.engine.abort(request_id)
+
+    # ---- convenience ---------------------------------------------------------------------------------------
+    def generate(self, prompts, max_new_tokens: int = 32, **sampling) -> list:
+        """Generate for a list of prompts (each a list of token ids); returns the generated ids of each."""
+        ids = [self.add_request(p, max_new_tokens, **sampling) for p in prompts]
+        self.run_until_complete()
+        return [self.get_result(i) for i in ids]

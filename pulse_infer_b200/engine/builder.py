@@ -37,7 +37,8 @@ def head_dims_of(model: DecoderModel) -> list:
 def build_runner(model_dir: str | None = None, *, config=None, seed: int | None = None, dtype: str = "bfloat16",
                  device="cuda:0", page_size: int = 16, num_pages: int | None = None, max_tokens: int | None = None,
                  max_requests: int = 64, max_tokens_per_request: int | None = None,
-                 max_tokens_per_step: int | None = None, attention_impl: str = "auto", **spec_options) -> ModelRunner:
+                 max_tokens_per_step: int | None = None, attention_impl: str = "auto",
+                 use_cuda_graphs: bool = False, **spec_options) -> ModelRunner:
     """From a model folder (``model_dir``) or from a configuration plus a seed (random weights on the
     device) to a ready step function.  The page pool holds ``num_pages`` pages per layer group, or
     enough for ``max_tokens`` tokens."""
@@ -62,6 +63,6 @@ def build_runner(model_dir: str | None = None, *, config=None, seed: int | None 
         per_request = max_tokens_per_request or min(model.spec.max_position, num_pages * page_size)
         cache = CacheManager(model.cache_specs(), model.state_specs(), page_size, num_pages, max_requests,
                              per_request, dtype=runtime.act_dtype, device=device)
-    runner = ModelRunner(model, cache, runtime, max_tokens_per_step)
+    runner = ModelRunner(model, cache, runtime, max_tokens_per_step, use_cuda_graphs)
     runner.config = config
     return runner

@@ -29,6 +29,7 @@ class Segment:
     # filled in by the step function from the cache manager
     slot: int = -1
     start: int = -1
+    offset: int = -1      # row of the segment's first token in the step's flat token list
 
 
 @dataclass
@@ -97,6 +98,7 @@ class StepContext:
         at, w = 0, 0
         for i, s in enumerate(segments):
             n = len(s.tokens)
+            s.offset = at
             tok[at:at + n] = s.tokens
             pos[at:at + n] = np.arange(s.start, s.start + n, dtype=np.int32)
             tslot[at:at + n] = s.slot

@@ -1,0 +1,97 @@
+"""Decode steps as CUDA graphs.
+
+A step that holds only single decoded tokens launches a few hundred small kernels; at batch 1 their
+launch cost exceeds their run time.  Such a step is captured once per (number of requests, bound on the
+number of key ranges) and replayed: the metadata buffer, the block tables and the output live at fixed
+addresses and are refilled in place before each replay.  The captured work is exactly what the eager
+step runs (same model code, same kernels).  The reference launches everything eagerly on the null
+stream (``src/ops/rope.cpp:231``, ``src/ops/matmul.cpp:115``).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .context import StepContext
+
+
+def _pow2_at_least(n: int) -> int:
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
+class DecodeGraph:
+    def __init__(self, runner, num_requests: int, splits_bound: int):
+        self.runner = runner
+        self.num_requests = num_requests
+        self.splits_bound = splits_bound
+        device = runner.runtime.device
+        self.layout = StepContext.layout(num_requests, num_requests, num_requests)
+        total = self.layout["_total"][1]
+        # two pinned staging buffers used in turn: a buffer is not rewritten before its copy has run
+        self.hosts = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.copied = [None, None]
+        self.turn = 0
+        self.ctx = StepContext(runner.runtime, runner.cache)
+        self.ctx.buffer = torch.zeros(total, dtype=torch.int32, device=device)
+        self.ctx.error_count = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ctx.splits_bound = splits_bound
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+
+    def _refill(self, segments) -> None:
+        buf, lay, (T, R, W) = StepContext.pack(segments)
+        assert lay == self.layout
+        i = self.turn
+        self.turn ^= 1
+        if self.copied[i] is not None:
+            self.copied[i].synchronize()
+        self.hosts[i].numpy()[:] = buf
+        self.ctx.buffer.copy_(self.hosts[i], non_blocking=True)
+        self.copied[i] = torch.cuda.Event()
+        self.copied[i].record()
+        self.ctx._bind(segments, lay, T, R, W)
+
+    def run(self, segments) -> torch.Tensor:
+        self._refill(segments)
+        if self.graph is None:
+            model = self.runner.model
+            # once eagerly (library initialisation, kernel attributes), then capture the same work
+            model.forward(self.ctx)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.kernels.LAUNCHES
+            with torch.cuda.graph(graph):
+                self.logits = model.forward(self.ctx)
+            self.launches_per_replay = ops.kernels.LAUNCHES - before
+            self.graph = graph
+        self.graph.replay()
+        ops.kernels.count_launches(self.launches_per_replay)
+        return self.logits
+
+
+class DecodeGraphs:
+    """The captured decode steps of one runner, made on demand, a bounded number kept."""
+
+    def __init__(self, runner, max_graphs: int = 96):
+        self.runner = runner
+        self.max_graphs = max_graphs
+        self.graphs: dict = {}
+
+    def eligible(self, segments) -> bool:
+        return all(len(s.tokens) == 1 and list(s.want) == [0] for s in segments)
+
+    def run(self, segments) -> torch.Tensor:
+        windows = {cs.window for cs in self.runner.model.cache_specs() if cs is not None}
+        pos_max = max(s.start for s in segments)
+        need = max(ops.attention_num_splits(pos_max, w) for w in windows) if windows else 1
+        key = (len(segments), _pow2_at_least(need))
+        g = self.graphs.get(key)
+        if g is None:
+            if len(self.graphs) >= self.max_graphs:
+                self.graphs.pop(next(iter(self.graphs)))
+            g = DecodeGraph(self.runner, key[0], key[1])
+            self.graphs[key] = g
+        return g.run(segments)

@@ -24,7 +24,8 @@ class StepError(ValueError):
 
 
 class ModelRunner:
-    def __init__(self, model, cache_manager: CacheManager, runtime, max_tokens_per_step: int | None = None):
+    def __init__(self, model, cache_manager: CacheManager, runtime, max_tokens_per_step: int | None = None,
+                 use_cuda_graphs: bool = False):
         self.model = model
         self.cache = cache_manager
         self.runtime = runtime
@@ -32,6 +33,10 @@ class ModelRunner:
         self.vocab_size = model.spec.vocab_size
         self.max_position = model.spec.max_position
         self._last_ctx: StepContext | None = None
+        self.graphs = None
+        if use_cuda_graphs:
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self)
 
     # ---- requests ------------------------------------------------------------------------------------
     def open(self, request_id) -> int:
@@ -74,11 +79,16 @@ class ModelRunner:
         [number of wanted places, vocab] in the order of the segments and of their ``want`` lists."""
         self.prepare(segments)
         self.cache.sync_tables()
-        ctx = StepContext.build(segments, self.runtime, self.cache)
-        logits = self.model.forward(ctx)
+        if self.graphs is not None and self.graphs.eligible(segments):
+            logits = self.graphs.run(segments)      # valid until the next captured step runs
+            ctx = None
+        else:
+            ctx = StepContext.build(segments, self.runtime, self.cache)
+            logits = self.model.forward(ctx)
         for s in segments:
             self.cache.commit(s.request_id, s.start + len(s.tokens))
-        self._last_ctx = ctx
+        if ctx is not None:
+            self._last_ctx = ctx
         return logits
 
     def check_device_errors(self) -> None:

@@ -20,6 +20,12 @@ from ..csrc import build
 F32, BF16 = 0, 1
 SPLIT_KEYS = 256          # keys per range of the split decode attention (a multiple of the 64-key tile)
 _LIBS: dict = {}
+LAUNCHES = 0              # kernels of this repository launched through these wrappers (graph replays add theirs)
+
+
+def count_launches(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
 
 
 class KernelError(RuntimeError):
@@ -40,7 +46,9 @@ def _lib(name: str, head_dim: int | None = None) -> ctypes.CDLL:
     return lib
 
 
-def _check(lib, rc: int, what: str) -> None:
+def _check(lib, rc: int, what: str, launches: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += launches
     if rc != 0:
         raise KernelError(f"{what} failed (code {rc}): {lib.pi_last_error().decode(errors='replace')}")
 
@@ -242,7 +250,8 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
         _p(seg_slot), _p(seg_start), _p(seg_len), _p(token_seg), _p(out), _p(part_acc), _p(part_ml), c_int(max_splits),
         c_int(split_keys), c_int(num_tokens), c_int(num_segments), c_int(max_seg_len), c_int(1 if has_prompt else 0),
         c_int(1 if has_decode else 0), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale),
-        _stream()), "attention_mma")
+        _stream()), "attention_mma",
+        launches=int(has_prompt) + int(has_decode) + int(has_decode and max_splits > 1))
     return out
 
 

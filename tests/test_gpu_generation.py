@@ -1,0 +1,357 @@
+"""Generation through the Python entry point and the command line, the parts of a layer alone, and a
+toy mixer with state of its own that is registered from here without touching the framework."""
+import dataclasses
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from gpu_util import need_gpu
+from helpers import load_plain, random_tokens
+from tiny_configs import CONFIGS, SEEDS
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _plain_generate(cfg, w, prompt, max_new, temperature=0.0, top_k=0, top_p=0.0, seed=0, eos=()):
+    toks, out = list(prompt), []
+    for i in range(max_new):
+        logits = plain_model.forward(cfg, w, toks)[-1]
+        t = plain_model.sample(logits, temperature, top_k, top_p, seed, i)
+        out.append(t); toks.append(t)
+        if t in eos:
+            break
+    return out
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_float32_config_a(model_folders, graphs):
+    """Tiny A: prompts of 5 and 17 tokens, 8 greedy steps, through Engine.generate."""
+    need_gpu()
+    from pulse_infer_b200 import Engine
+    folder, cfg = model_folders["A"], CONFIGS["A"]
+    pc, pw = load_plain(folder)
+    prompts = [random_tokens(1, 5, cfg.vocab_size), random_tokens(2, 17, cfg.vocab_size)]
+    engine = Engine(folder, dtype="float32", page_size=8, num_pages=16, max_batch_size=2, chunk_size=256,
+                    use_cuda_graphs=graphs)
+    got = engine.generate(prompts, max_new_tokens=8, ignore_eos=True)
+    want = [_plain_generate(pc, pw, p, 8) for p in prompts]
+    assert got == want
+    st = engine.get_stats()
+    assert st.num_finished == 2 and st.decode_tokens == 14 and list(st.free_pages) == [16]
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_sampled_generation_mixed_batch_config_b(model_folders, graphs):
+    """Tiny B: three requests (prompts 1, 23, 40), portions of 7, 12 tokens at temperature 0.8, seeded."""
+    need_gpu()
+    from pulse_infer_b200 import Engine
+    folder, cfg = model_folders["B"], CONFIGS["B"]
+    pc, pw = load_plain(folder)
+    prompts = [random_tokens(s, n, cfg.vocab_size) for s, n in ((1, 1), (2, 23), (3, 40))]
+    engine = Engine(folder, dtype="float32", page_size=16, num_pages=12, max_batch_size=3, chunk_size=7,
+                    use_cuda_graphs=graphs)
+    ids = [engine.add_request(p, 12, temperature=0.8, seed=100 + i, ignore_eos=True) for i, p in enumerate(prompts)]
+    engine.run_until_complete()
+    for i, (rid, p) in enumerate(zip(ids, prompts)):
+        assert engine.get_result(rid) == _plain_generate(pc, pw, p, 12, temperature=0.8, seed=100 + i)
+
+
+def test_generation_survives_preemption_and_eos(model_folders):
+    """So few pages that requests are preempted and recomputed; tokens are the same as with plenty."""
+    need_gpu()
+    from pulse_infer_b200 import Engine
+    folder, cfg = model_folders["C"], CONFIGS["C"]
+    prompts = [random_tokens(20 + i, n, cfg.vocab_size) for i, n in enumerate((30, 18, 25, 9))]
+    outs = {}
+    for pages in (64, 7):
+        engine = Engine(folder, dtype="float32", page_size=8, num_pages=pages, max_batch_size=3, chunk_size=16,
+                        max_tokens_per_request=128)
+        ids = [engine.add_request(p, 20, temperature=0.7, top_k=50, top_p=0.9, seed=i, ignore_eos=True)
+               for i, p in enumerate(prompts)]
+        engine.run_until_complete()
+        outs[pages] = [engine.get_result(i) for i in ids]
+        if pages == 7:
+            assert engine.get_stats().num_preemptions > 0
+        engine.runner.cache.check_invariants()
+    assert outs[64] == outs[7] and all(len(o) == 20 for o in outs[64])
+    # EOS: take a token the first request generates and declare it the stop token
+    stop = outs[64][0][5]
+    engine = Engine(folder, dtype="float32", page_size=8, num_pages=64, max_batch_size=3, max_tokens_per_request=128)
+    engine.engine.eos_token_ids = (stop,)
+    rid = engine.add_request(prompts[0], 20, temperature=0.7, top_k=50, top_p=0.9, seed=0)
+    engine.run_until_complete()
+    first = outs[64][0].index(stop)
+    assert engine.get_result(rid) == outs[64][0][:first + 1] and engine.get_request(rid).finish_reason == "eos"
+
+
+def test_bfloat16_greedy_tokens_are_top_tokens(model_folders):
+    need_gpu()
+    from pulse_infer_b200 import Engine
+    folder, cfg = model_folders["B"], CONFIGS["B"]
+    pc, pw = load_plain(folder)
+    prompts = [random_tokens(5, 33, cfg.vocab_size), random_tokens(6, 4, cfg.vocab_size)]
+    for graphs in (False, True):
+        engine = Engine(folder, dtype="bfloat16", page_size=16, num_pages=16, max_batch_size=2, use_cuda_graphs=graphs)
+        outs = engine.generate(prompts, max_new_tokens=10, ignore_eos=True)
+        for p, o in zip(prompts, outs):
+            ref = plain_model.forward(pc, pw, p + o)
+            for i, t in enumerate(o):
+                row = ref[len(p) + i - 1]
+                assert row[t] >= row.max() - 0.02 * np.abs(row).max()
+
+
+def test_command_line_programs(model_folders, tmp_path):
+    need_gpu()
+    folder = model_folders["A"]
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen3_continuous_batch_demo"), folder,
+                          "--dtype", "float32", "--prompt-len", "9", "--prompt-len", "21", "--max-new-tokens", "6",
+                          "--ignore-eos", "--chunk-size", "8"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    pc, pw = load_plain(folder)
+    for i, (rec, n) in enumerate(zip(lines, (9, 21))):
+        prompt = [int(t) for t in np.random.RandomState(i).randint(0, CONFIGS["A"].vocab_size, size=n)]
+        assert rec["generated"] == _plain_generate(pc, pw, prompt, 6)
+    assert "tokens/s" in out.stdout
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen3_infer"), folder, "--prompt-ids", "1,2,3,4",
+                          "--max-new-tokens", "5", "--ignore-eos", "--seed", "3"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rec = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][0])
+    assert len(rec["generated"]) == 5 and "tokens/s" in out.stdout
+
+
+# ---- each part of a layer alone ----------------------------------------------------------------------------
+def _ctx_for(segs, cache_specs, runtime, page_size=8, state_specs=None):
+    """A cache manager and a step context for hand-made segments [(request id, start, tokens)]."""
+    from pulse_infer_b200.cache import CacheManager
+    from pulse_infer_b200.engine import Segment, StepContext
+    cm = CacheManager(cache_specs, state_specs or [None] * len(cache_specs), page_size, 32, 4, 256,
+                      dtype=runtime.act_dtype, device=runtime.device)
+    segments = []
+    for rid, start, toks in segs:
+        cm.open(rid); cm.reserve(rid, start + len(toks)); cm.commit(rid, start)
+        s = Segment(rid, toks, [len(toks) - 1]); s.slot = cm.slot(rid); s.start = start
+        segments.append(s)
+    cm.sync_tables()
+    return cm, StepContext.build(segments, runtime, cm)
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+def test_parts_alone(mode):
+    dev = need_gpu()
+    from pulse_infer_b200.parts import Runtime, build_part
+    rt = Runtime(dev, mode)
+    dt = rt.act_dtype
+    tol = 1e-5 if mode == "float32" else 2e-2
+    g = torch.Generator().manual_seed(0)
+    H, I, nq, nkv, d, T = 72, 200, 6, 3, 32, 11
+    _, ctx = _ctx_for([("a", 0, list(range(T)))], [None], rt)
+
+    norm = build_part("norm", "rmsnorm", dict(size=H, eps=1e-5))
+    wn = (1 + 0.1 * torch.randn(H, generator=g)).to(dt)
+    norm.load({"weight": wn.to(dev)}, rt)
+    h = torch.randn(T, H, generator=g)
+    got = norm.forward(h.clone().to(dev), ctx).cpu().double().numpy()
+    want = plain_model.rms_norm(h.double().numpy(), wn.double().numpy(), 1e-5)
+    assert np.abs(got - want).max() <= tol * np.abs(want).max()
+
+    ff = build_part("feed_forward", "swiglu", dict(hidden_size=H, intermediate_size=I))
+    ws = {k: (torch.randn(*shape, generator=g) * 0.1).to(dt) for k, shape in
+          (("gate_proj.weight", (I, H)), ("up_proj.weight", (I, H)), ("down_proj.weight", (H, I)))}
+    ff.load({k: v.to(dev) for k, v in ws.items()}, rt)
+    x = torch.randn(T, H, generator=g).to(dt)
+    got = ff.forward(x.to(dev), ctx).cpu().double().numpy()
+    want = plain_model.swiglu(x.double().numpy(), *[ws[k].double().numpy() for k in ws])
+    assert np.abs(got - want).max() <= tol * np.abs(want).max()
+
+    rope = build_part("position_encoding", "rotary", dict(theta=5000.0, rotary_dim=d, pairing="half"))
+    _, ctx2 = _ctx_for([("a", 37, list(range(T)))], [None], rt)
+    tab = rope.prepare(ctx2)
+    ang = np.arange(37, 37 + T)[:, None] / np.power(5000.0, 2.0 * np.arange(d // 2) / d)[None, :]
+    assert np.abs(tab["cos"].cpu().numpy() - np.cos(ang)).max() < 1e-6 and tab["adjacent"] is False
+
+    # attention part: a portion of 11 tokens at position 37 of a request whose first 37 tokens are in the cache
+    from pulse_infer_b200.parts.base import CacheSpec
+    for pairing, window in (("adjacent", None), ("half", 9)):
+        attn = build_part("mixer", "attention", dict(hidden_size=H, num_heads=nq, num_kv_heads=nkv, head_dim=d,
+                                                    qk_norm=True, norm_eps=1e-5, position="rot", window=window))
+        aw = {k: (torch.randn(*shape, generator=g) * 0.15).to(dt) for k, shape in
+              (("q_proj.weight", (nq * d, H)), ("k_proj.weight", (nkv * d, H)), ("v_proj.weight", (nkv * d, H)),
+               ("o_proj.weight", (H, nq * d)))}
+        aw["q_norm.weight"] = (1 + 0.1 * torch.randn(d, generator=g)).to(dt)
+        aw["k_norm.weight"] = (1 + 0.1 * torch.randn(d, generator=g)).to(dt)
+        attn.load({k: v.to(dev) for k, v in aw.items()}, rt)
+        rope = build_part("position_encoding", "rotary", dict(theta=5000.0, rotary_dim=d, pairing=pairing))
+        xs = torch.randn(48, H, generator=g).to(dt)
+        cm, ctx_a = _ctx_for([("a", 0, list(range(37)))], [attn.cache_spec()], rt)
+        ctx_a.position_data = {"rot": rope.prepare(ctx_a)}
+        y1 = attn.forward(xs[:37].to(dev), ctx_a, ctx_a.cache_view(0, 0))
+        cm.commit("a", 37)
+        from pulse_infer_b200.engine import Segment, StepContext
+        seg = Segment("a", list(range(11)), [10]); seg.slot = cm.slot("a"); seg.start = 37
+        cm.reserve("a", 48); cm.sync_tables()
+        ctx_b = StepContext.build([seg], rt, cm)
+        ctx_b.position_data = {"rot": rope.prepare(ctx_b)}
+        y2 = attn.forward(xs[37:].to(dev), ctx_b, ctx_b.cache_view(0, 0))
+        got = torch.cat([y1, y2]).cpu().double().numpy()
+        xd = xs.double().numpy()
+        wd = {k: v.double().numpy() for k, v in aw.items()}
+        pos = np.arange(48)
+        q = plain_model.rope(plain_model.rms_norm((xd @ wd["q_proj.weight"].T).reshape(48, nq, d), wd["q_norm.weight"], 1e-5), pos, 5000.0, d, pairing)
+        k = plain_model.rope(plain_model.rms_norm((xd @ wd["k_proj.weight"].T).reshape(48, nkv, d), wd["k_norm.weight"], 1e-5), pos, 5000.0, d, pairing)
+        v = (xd @ wd["v_proj.weight"].T).reshape(48, nkv, d)
+        want = plain_model.attention(q, k, v, window).reshape(48, nq * d) @ wd["o_proj.weight"].T
+        assert np.abs(got - want).max() <= tol * np.abs(want).max(), (pairing, window)
+
+
+# ---- a toy mixer with state, registered from the test ----------------------------------------------------------
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A new architecture whose second layer's mixer is a decaying running sum kept in the per-request
+    state slot.  Nothing under pulse_infer_b200/ is changed: the mixer, the architecture and its
+    configuration are registered here."""
+    dev = need_gpu()
+    from pulse_infer_b200 import ops
+    from pulse_infer_b200.config import Qwen3Config, register_architecture
+    from pulse_infer_b200.engine import Segment, build_runner
+    from pulse_infer_b200.models.qwen3 import build_qwen3_spec
+    from pulse_infer_b200.models.spec import PartSpec
+    from pulse_infer_b200.parts.base import MIXERS, Mixer, StateSpec, TensorSpec, register_part
+    from pulse_infer_b200.weights import write_random_model
+
+    DECAY = 0.75
+
+    class DecaySum(Mixer):
+        """s_t = decay * s_(t-1) + x_t per request; y_t = W s_t.  State: s, one vector per request."""
+
+        def __init__(self, hidden_size, decay):
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def tensor_specs(self):
+            return {"mix.weight": TensorSpec((self.hidden_size, self.hidden_size))}
+
+        def state_spec(self):
+            return StateSpec((self.hidden_size,), torch.float32)
+
+        def load(self, tensors, runtime):
+            self.w = tensors["mix.weight"]
+            self._tensors = {"w": self.w}
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            for seg in ctx.segments:
+                s = cache.state[seg.slot]
+                for i in range(len(seg.tokens)):
+                    s = self.decay * s + x[seg.offset + i].float()
+                    out[seg.offset + i] = s
+                cache.state[seg.slot] = s
+            return ops.linear(out.to(x.dtype), self.w, ctx.act_dtype)
+
+    if "decay_sum" not in MIXERS:
+        register_part("mixer", "decay_sum")(DecaySum)
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig(Qwen3Config):
+        pass
+
+    def build_toy_spec(config):
+        spec = build_qwen3_spec(config)
+        layers = list(spec.layers)
+        layers[1] = dataclasses.replace(layers[1], mixer=PartSpec(
+            "decay_sum", dict(hidden_size=config.hidden_size, decay=DECAY), "model.layers.1.toy."))
+        order = tuple(dataclasses.replace(e, cache=None) if e.layer == 1 else e for e in spec.order)
+        return dataclasses.replace(spec, layers=tuple(layers), order=order)
+
+    register_architecture("ToyStateForCausalLM", ToyConfig, build_toy_spec, replace=True)
+    cfg = dataclasses.replace(CONFIGS["B"], architecture="ToyStateForCausalLM")
+    cfg = ToyConfig(**{f.name: getattr(cfg, f.name) for f in dataclasses.fields(cfg)})
+    folder = write_random_model(cfg, 5, str(tmp_path / "toy"), dtype="bfloat16")
+    pc, pw = load_plain(folder)
+    assert "model.layers.1.toy.mix.weight" in pw and "model.layers.1.self_attn.q_proj.weight" not in pw
+
+    def plain_toy(tokens):
+        w = {k: np.asarray(v, dtype=np.float64) for k, v in pw.items()}
+        positions = np.arange(len(tokens))
+        h = plain_model.embedding(w["model.embed_tokens.weight"], tokens)
+        for layer in range(pc["num_hidden_layers"]):
+            prefix = f"model.layers.{layer}."
+            if layer != 1:
+                h, _ = plain_model.decoder_layer(h, w, prefix, pc, positions)
+                continue
+            x = plain_model.rms_norm(h, w[prefix + "input_layernorm.weight"], pc["rms_norm_eps"])
+            s, ys = np.zeros(h.shape[1]), []
+            for t in range(len(tokens)):
+                s = DECAY * s + x[t]
+                ys.append(s.copy())
+            h = h + plain_model.linear(np.stack(ys), w[prefix + "toy.mix.weight"])
+            x = plain_model.rms_norm(h, w[prefix + "post_attention_layernorm.weight"], pc["rms_norm_eps"])
+            h = h + plain_model.swiglu(x, w[prefix + "mlp.gate_proj.weight"], w[prefix + "mlp.up_proj.weight"],
+                                       w[prefix + "mlp.down_proj.weight"])
+        x = plain_model.rms_norm(h, w["model.norm.weight"], pc["rms_norm_eps"])
+        return plain_model.linear(x, w["lm_head.weight"])
+
+    runner = build_runner(folder, dtype="float32", device="cuda:0", page_size=8, num_pages=32, max_requests=3,
+                          max_tokens_per_request=128)
+    assert 1 in runner.cache.state and runner.cache.state[1].shape == (3, cfg.hidden_size)
+    assert len(runner.cache.groups) == 1 and runner.cache.groups[0].cache_indices == [0, 2]
+    reqs = {"a": random_tokens(1, 40, cfg.vocab_size), "b": random_tokens(2, 23, cfg.vocab_size)}
+    want = {k: plain_toy(v) for k, v in reqs.items()}
+    runner.open("a"); runner.open("b")
+    plan = [[("a", 0, 13), ("b", 0, 2)], [("a", 13, 14), ("b", 2, 20)], [("a", 14, 15)], [("b", 20, 21), ("a", 15, 40)],
+            [("b", 21, 23)]]
+    for step in plan:
+        logits = runner.step([Segment(r, reqs[r][a:b], list(range(b - a))) for r, a, b in step]).cpu().double().numpy()
+        ref = np.concatenate([want[r][a:b] for r, a, b in step])
+        assert np.abs(logits - ref).max() <= 2e-5 * np.abs(ref).max()
+    # a slot that is reused starts from zero state
+    runner.close("a"); runner.open("c")
+    logits = runner.step([Segment("c", reqs["b"], list(range(23)))]).cpu().double().numpy()
+    assert np.abs(logits - want["b"]).max() <= 2e-5 * np.abs(want["b"]).max()
+
+
+def test_layer_order_as_data_repeat_and_shared_cache(model_folders, tmp_path):
+    """The order in which layers run is a list: here layer 0 runs twice (with a cache of its own each
+    time) and a last layer without key/value projections reads the cache that layer 1 filled."""
+    dev = need_gpu()
+    from pulse_infer_b200.config import Qwen3Config, register_architecture
+    from pulse_infer_b200.engine import Segment, build_runner
+    from pulse_infer_b200.models.qwen3 import build_qwen3_spec
+    from pulse_infer_b200.models.spec import ScheduleEntry
+    from pulse_infer_b200.weights import write_random_model
+
+    @dataclasses.dataclass(frozen=True)
+    class LoopConfig(Qwen3Config):
+        pass
+
+    def build_loop_spec(config):
+        spec = build_qwen3_spec(config)
+        layers = list(spec.layers)
+        last = len(layers) - 1
+        reader = dataclasses.replace(layers[last].mixer, params={**layers[last].mixer.params, "writes_cache": False})
+        layers[last] = dataclasses.replace(layers[last], mixer=reader)
+        order = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(last, 1))
+        return dataclasses.replace(spec, layers=tuple(layers), order=order)
+
+    register_architecture("LoopForCausalLM", LoopConfig, build_loop_spec, replace=True)
+    base = CONFIGS["B"]
+    cfg = LoopConfig(**{**{f.name: getattr(base, f.name) for f in dataclasses.fields(base)},
+                        "architecture": "LoopForCausalLM"})
+    folder = write_random_model(cfg, 9, str(tmp_path / "loop"), dtype="bfloat16")
+    pc, pw = load_plain(folder)
+    assert "model.layers.2.self_attn.k_proj.weight" not in pw
+    toks = random_tokens(4, 45, cfg.vocab_size)
+    want = plain_model.forward(pc, pw, toks, order=[(0, 0), (1, 1), (0, 2), (2, 1)])
+    for dtype, tol in (("float32", 2e-5), ("bfloat16", 2e-2)):
+        runner = build_runner(folder, dtype=dtype, device="cuda:0", page_size=16, num_pages=16, max_requests=2,
+                              max_tokens_per_request=64)
+        runner.open("a")
+        got = [runner.step([Segment("a", toks[a:b], list(range(b - a)))]) for a, b in ((0, 19), (19, 21), (21, 44), (44, 45))]
+        got = torch.cat(got).cpu().double().numpy()
+        assert np.abs(got - want).max() <= tol * np.abs(want).max()

@@ -90,7 +90,7 @@ def test_qk_norm_rope_write(dtype, nq, nkv, d, rot, adjacent, page):
     kw = (1 + 0.2 * torch.randn(d, generator=g)).to(dtype)
     eps, theta = 1e-5, 10000.0
     pages = 24
-    table = torch.full((3, 8), -1, dtype=torch.int32)
+    table = torch.full((3, 16), -1, dtype=torch.int32)
     perm = torch.randperm(pages, generator=g).tolist()
     for slot, start, n in segs:
         for i in range((start + n + page - 1) // page):
