@@ -33,6 +33,13 @@ CONTEXT = 4096
 PROMPT = 2048
 PAGE = 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+PROFILER_RANGE = False      # --only: bracket the timed steps with cudaProfilerStart/Stop (ncu --profile-from-start off)
+
+
+def _profiler(start: bool) -> None:
+    if PROFILER_RANGE:
+        import torch
+        (torch.cuda.profiler.start if start else torch.cuda.profiler.stop)()
 
 
 def load_peaks():
@@ -124,7 +131,7 @@ def prefill_flops(cfg, T: int) -> float:
     return linear + attention
 
 
-def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: bool):
+def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: bool, context: int | None = None):
     """``steps`` timed decode steps of ``batch`` requests whose prompts were 2,048 random ids, ending at
     context 4096.  through_api=False: the step function with device-side argmax and pre-drawn input
     tokens (no host round trip between steps).  through_api=True: Engine.step() - every step takes host
@@ -136,6 +143,7 @@ def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: 
     from pulse_infer_b200.engine.context import StepContext
     vocab = engine.config.vocab_size
     runner = engine.runner
+    CONTEXT = context or globals()["CONTEXT"]
     prompts = [[int(t) for t in rng.randint(0, vocab, size=PROMPT)] for _ in range(batch)]
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     h2d = StepContext.layout(batch, batch, batch)["_total"][1] * 4
@@ -179,11 +187,13 @@ def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: 
             one(k)
         torch.cuda.synchronize()
         before = ops.kernels.LAUNCHES
+        _profiler(True)
         ev0.record()
         for k in range(advance + warmup, advance + warmup + steps):
             one(k)
         ev1.record()
         torch.cuda.synchronize()
+        _profiler(False)
         assert all(runner.cache.length(rid) == CONTEXT for rid in rids)
         mean_ctx = CONTEXT - steps / 2.0
         d2h = 0
@@ -204,20 +214,46 @@ def timed_prefill(engine, rng, repeats: int = 3):
         runner.open(("prefill", i))
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        if i == repeats:
+            _profiler(True)
         ev0.record()
         runner.step([Segment(("prefill", i), tokens, [PROMPT - 1])])
         ev1.record()
         torch.cuda.synchronize()
+        if i == repeats:
+            _profiler(False)
         runner.close(("prefill", i))
         if i > 0:                       # the first run warms up
             times.append(ev0.elapsed_time(ev1))
     return statistics.median(times)
 
 
+def make_engine(cfg, max_batch: int, graphs: bool = True):
+    from pulse_infer_b200 import Engine
+    return Engine(None, config=cfg, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=max_batch * (CONTEXT + 256),
+                  max_batch_size=max_batch, chunk_size=PROMPT, max_tokens_per_step=PROMPT + max_batch,
+                  max_tokens_per_request=CONTEXT + 256, use_cuda_graphs=graphs)
+
+
+def run_part(args) -> dict:
+    """A short run of one phase only (for profilers): --only decode | prefill, usually with few layers."""
+    import numpy as np
+    global PROFILER_RANGE
+    PROFILER_RANGE = True
+    cfg = make_config(args.layers or FULL_LAYERS)
+    rng = np.random.RandomState(0)
+    engine = make_engine(cfg, args.batch, graphs=not args.no_graphs)
+    if args.only == "prefill":
+        ms = timed_prefill(engine, rng, repeats=max(1, args.steps))
+        return {"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": PROMPT, "ms": round(ms, 3)}
+    ms, launches, ctx, _, _ = timed_decode(engine, args.batch, args.steps, args.warmup, rng, False, context=args.context)
+    return {"only": "decode", "layers": cfg.num_hidden_layers, "batch": args.batch, "context": args.context,
+            "ms_per_step": round(ms, 4), "gpu_launches": launches, "cuda_graphs": not args.no_graphs}
+
+
 def run_ours(args) -> dict:
     import numpy as np
     import torch
-    from pulse_infer_b200 import Engine
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
     peaks, peak_source = load_peaks()
@@ -227,9 +263,7 @@ def run_ours(args) -> dict:
     batches = sorted({1, 8, 64} | {args.batch})
     max_batch = max(batches)
     t_build = time.time()
-    engine = Engine(None, config=cfg, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=max_batch * (CONTEXT + 256),
-                    max_batch_size=max_batch, chunk_size=PROMPT, max_tokens_per_step=PROMPT + max_batch,
-                    max_tokens_per_request=CONTEXT + 256, use_cuda_graphs=True)
+    engine = make_engine(cfg, max_batch)
     build_s = time.time() - t_build
     wbytes = weight_bytes_per_step(cfg)
 
@@ -289,6 +323,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the 36 of the shape (named in config)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one phase only (for profilers)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: the context the timed steps end at")
+    ap.add_argument("--no-graphs", action="store_true", help="with --only: launch decode steps eagerly")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a C++/CMake project without setup.py or "
@@ -298,6 +335,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, only --gpus 1")
         return 2
+    if args.only:
+        print(json.dumps(run_part(args)))
+        return 0
     args.warmup = max(args.warmup, 3)
     result = run_ours(args)
     print(json.dumps(result))
