@@ -20,6 +20,7 @@
 // absolute position, online softmax, out = acc / sum, pages with a negative id are skipped).
 #include <math.h>
 
+#include "attention_noalloc.h"
 #include "common.cuh"
 
 #ifndef PI_HEAD_DIM
@@ -463,4 +464,68 @@ PI_EXPORT int pi_attention_mma(const void* q, int q_stride, const void* kcache, 
         }
     }
     return rc;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The same attention for callers that must not allocate (see attention_noalloc.h).
+// The partial results of the split decode attention live in a fixed array in device memory that is
+// part of this library's image: every GPU that loads the library holds PI_NOALLOC_SCRATCH_BYTES of it
+// until the process exits.
+// ---------------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_noalloc_scratch[PI_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+// Device addresses of g_noalloc_scratch, looked up once per device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use: the address comes from
+// cudaGetSymbolAddress, asked while that device is current.
+#define PI_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[PI_NOALLOC_MAX_DEVICES] = {nullptr};
+
+static int noalloc_scratch(float** out) {
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        snprintf(g_pi_error, sizeof(g_pi_error), "pi_attention_mma_noalloc: cudaGetDevice: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
+    if (device < 0 || device >= PI_NOALLOC_MAX_DEVICES)
+        return pi_refuse("pi_attention_mma_noalloc: device index %d is beyond the %d this library tracks", device, PI_NOALLOC_MAX_DEVICES);
+    if (g_noalloc_ptr[device] == nullptr) {
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess || ptr == nullptr) {
+            snprintf(g_pi_error, sizeof(g_pi_error), "pi_attention_mma_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+            return err != cudaSuccess ? (int)err : -1;
+        }
+        g_noalloc_ptr[device] = (float*)ptr;
+    }
+    *out = g_noalloc_ptr[device];
+    return 0;
+}
+
+PI_EXPORT int pi_attention_noalloc_scratch_bytes() { return PI_NOALLOC_SCRATCH_BYTES; }
+
+PI_EXPORT int pi_attention_mma_noalloc(const void* q, int q_stride, const void* kcache, const void* vcache,
+                                       const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                                       const int* seg_start, const int* seg_len, const int* token_seg, void* out,
+                                       int max_splits, int split_keys, int num_tokens, int num_segments,
+                                       int max_seg_len, int has_prompt, int has_decode, int nq, int nkv, int page_size,
+                                       int window, float scale, cudaStream_t stream) {
+    if (num_tokens <= 0 || num_segments <= 0) return 0;
+    if (max_splits < 1) return pi_refuse("pi_attention_mma_noalloc: max_splits=%d must be at least 1", max_splits);
+    // partial outputs [tokens * heads, max_splits, D] followed by (max, sum) pairs [tokens * heads, max_splits, 2]
+    const unsigned long long rows = (unsigned long long)num_tokens * (unsigned long long)(nq > 0 ? nq : 0);
+    const unsigned long long acc_floats = rows * (unsigned long long)max_splits * PI_HEAD_DIM;
+    const unsigned long long need = (acc_floats + rows * (unsigned long long)max_splits * 2ull) * sizeof(float);
+    if (need > (unsigned long long)PI_NOALLOC_SCRATCH_BYTES)
+        return pi_refuse("pi_attention_mma_noalloc: %d tokens x %d heads x %d key ranges need %llu bytes of scratch, the fixed "
+                         "array holds %d; use pi_attention_mma with scratch of your own", num_tokens, nq, max_splits, need,
+                         PI_NOALLOC_SCRATCH_BYTES);
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    // Nothing in the scratch has to start at zero: a (row, range) entry is written by the attention kernel
+    // before the merge kernel reads it, and entries of ranges a request does not use are never read.
+    return pi_attention_mma(q, q_stride, kcache, vcache, block_table, bt_stride, seg_off, seg_slot, seg_start, seg_len,
+                            token_seg, out, scratch, scratch + acc_floats, max_splits, split_keys, num_tokens,
+                            num_segments, max_seg_len, has_prompt, has_decode, nq, nkv, page_size, window, scale, stream);
 }

@@ -30,7 +30,7 @@ SOURCES = {
     "sampling": "sampling.cu",
 }
 ATTENTION_MMA_SOURCE = "attention_mma.cu"
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_noalloc.h"]
 
 _lock = threading.Lock()
 
