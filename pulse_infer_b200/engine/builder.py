@@ -49,7 +49,12 @@ def build_runner(model_dir: str | None = None, *, config=None, seed: int | None 
     elif config is None:
         raise ValueError("give a model folder or a configuration")
     model = build_model(config, runtime, **spec_options)
-    ops.preload(head_dims_of(model) if runtime.mode == "bfloat16" and attention_impl != "simple" else ())
+    fast = runtime.mode == "bfloat16" and attention_impl != "simple"
+    dims = head_dims_of(model)
+    specs = [cs for cs in model.cache_specs() if cs is not None]
+    needs_simple = not fast or any(cs.head_dim not in dims for cs in specs)
+    ops.preload(dims if fast else (), simple_attention=needs_simple and bool(specs),
+                float32_products=runtime.mode == "float32")
     with torch.cuda.device(device):
         if model_dir is not None:
             load_weights(model, model_dir, runtime)

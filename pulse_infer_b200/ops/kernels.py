@@ -81,10 +81,12 @@ def _need_contig(**tensors) -> None:
             raise KernelError(f"tensor '{name}' must be contiguous")
 
 
-def preload(head_dims=(), simple_attention: bool = True) -> None:
-    """Build and load what a model needs, so that the first step does not pay for it."""
-    for name in ("elementwise", "gemm_f32", "sampling"):
-        _lib(name)
+def preload(head_dims=(), simple_attention: bool = False, float32_products: bool = False) -> None:
+    """Build and load what a model needs, so that the first step does not pay for it.  Everything else
+    (sampling, for instance) is built when it is first called."""
+    _lib("elementwise")
+    if float32_products:
+        _lib("gemm_f32")
     if simple_attention:
         _lib("attention_simple")
     for d in head_dims:
