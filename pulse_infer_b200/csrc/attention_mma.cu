@@ -5,7 +5,7 @@
 // tile fetched through the block table is shared by all query heads of the group.  S = Q K^T and
 // O += P V run on mma.sync m16n8k16 (bf16 in, fp32 accumulate); the running maximum, the sums and the
 // rescaling are 32-bit (online softmax, exp2 of scores pre-multiplied by log2(e)/sqrt(d)).  Keys and
-// values arrive in shared memory by 16-byte cp.async through the page table, double-buffered.
+// values arrive in shared memory by 16-byte cp.async through the page table, two or three tiles deep.
 //
 //   prompt mode  (ROW_WARPS x 1 warps): each warp owns 16 rows and walks every key tile.
 //   decode mode  (1 x KEY_WARPS warps): the warps share 16 rows and each takes a quarter of every key
@@ -91,14 +91,14 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <int D, int ROW_WARPS, int KEY_WARPS>
+template <int D, int ROW_WARPS, int KEY_WARPS, int STAGES>
 __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(const AttnParams p) {
     constexpr int BM = ROW_WARPS * 16;
     constexpr int NTHREADS = ROW_WARPS * KEY_WARPS * 32;
     constexpr int LDS = D + 8;              // padded row length in elements: conflict-free ldmatrix
     constexpr int CHUNKS = D / 8;           // 16-byte chunks per row
     constexpr int KPW = BN / KEY_WARPS;     // keys of a tile that one warp handles
-    constexpr int STAGES = 2;
+    static_assert(STAGES == 2 || STAGES == 3, "two or three stages");
     static_assert(KPW % 16 == 0, "a warp needs whole k16 steps");
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
     bf16* Ks = Qs + BM * LDS;                                      // [STAGES][BN][LDS]
     bf16* Vs = Ks + STAGES * BN * LDS;                             // [STAGES][BN][LDS]
 
+    pdl_wait();
+    pdl_trigger(PDL_ATTENTION);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wr = warp / KEY_WARPS, wk = warp % KEY_WARPS;
     const int seg = blockIdx.x / p.tiles_per_seg, tile = blockIdx.x % p.tiles_per_seg;
@@ -148,22 +150,34 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
             cp_async16(Qs + r * LDS + c * 8, src, valid);
         }
     };
+    // Element offset of every key row of a tile inside the page pools, looked up through the block table by
+    // the first BN threads one tile ahead of the copies that use it (so neither the table lookup nor the
+    // divisions sit on the critical path); ~0 marks a row that does not exist.
+    __shared__ size_t row_off[2][BN];
+    static_assert(NTHREADS >= BN, "the first BN threads fill the row-offset table");
+    auto compute_rows = [&](int kt, int buf) {
+        if (tid < BN) {
+            const int j = kbegin + kt * BN + tid;
+            size_t off = ~(size_t)0;
+            if (kt < num_tiles && j < kend) {
+                const int page = table[j / p.page_size];
+                if (page >= 0) off = (((size_t)page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * D;
+            }
+            row_off[buf][tid] = off;
+        }
+    };
     auto load_kv = [&](int kt, int stage) {
-        const int k0 = kbegin + kt * BN;
         bf16* kd = Ks + stage * BN * LDS;
         bf16* vd = Vs + stage * BN * LDS;
+        const size_t* offs = row_off[kt & 1];
+#pragma unroll
         for (int idx = tid; idx < BN * CHUNKS; idx += NTHREADS) {
             const int r = idx / CHUNKS, c = idx % CHUNKS;
-            const int j = k0 + r;
-            bool valid = j < kend;
-            size_t off = 0;
-            if (valid) {
-                const int page = table[j / p.page_size];
-                valid = page >= 0;
-                if (valid) off = (((size_t)page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * D + c * 8;
-            }
-            cp_async16(kd + r * LDS + c * 8, p.kcache + off, valid);
-            cp_async16(vd + r * LDS + c * 8, p.vcache + off, valid);
+            const size_t off = offs[r];
+            const bool valid = off != ~(size_t)0;
+            const size_t src = valid ? off + c * 8 : 0;
+            cp_async16(kd + r * LDS + c * 8, p.kcache + src, valid);
+            cp_async16(vd + r * LDS + c * 8, p.vcache + src, valid);
         }
     };
 
@@ -184,10 +198,15 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
     // visibility bounds of the whole warp (uniform): used to skip tiles
     const int wrow_first = row0 + wr * 16;
     int warp_pos_max = -1, warp_lo_min = 0;
+    int warp_pos_min = -1, warp_lo_max = 0;   // a key range inside [warp_lo_max, warp_pos_min] needs no mask
     if (wrow_first < rows_total) {
         const int wrow_last = (wrow_first + 15 < rows_total ? wrow_first + 15 : rows_total - 1);
         warp_pos_max = start + wrow_last / G;
         warp_lo_min = window_lo(start + wrow_first / G, p.window);
+        if (wrow_first + 15 < rows_total) {   // all 16 rows exist
+            warp_pos_min = start + wrow_first / G;
+            warp_lo_max = window_lo(warp_pos_max, p.window);
+        }
     }
 
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
@@ -196,15 +215,26 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
     for (int i = 0; i < D / 8; ++i) { o[i][0] = 0.0f; o[i][1] = 0.0f; o[i][2] = 0.0f; o[i][3] = 0.0f; }
 
     // ---- pipeline ------------------------------------------------------------------------------------
+    // Tile t is copied STAGES-1 iterations before it is used; its row offsets are computed one iteration
+    // before that, into half (t & 1) of the table, which the copies of tile t-2 were the last to read.
+#pragma unroll
+    for (int t = 0; t < STAGES - 1; ++t) compute_rows(t, t & 1);
+    __syncthreads();
     load_q();
-    load_kv(0, 0);
-    cp_async_commit();
+#pragma unroll
+    for (int t = 0; t < STAGES - 1; ++t) {
+        if (t < num_tiles) load_kv(t, t);
+        cp_async_commit();
+    }
+    if (STAGES == 3) __syncthreads();  // half 0 is about to be rewritten
+    compute_rows(STAGES - 1, (STAGES - 1) & 1);
 
     for (int kt = 0; kt < num_tiles; ++kt) {
-        cp_async_wait<0>();
-        __syncthreads();  // tile kt (and Q) visible to all; everyone is done with the other stage
-        if (kt + 1 < num_tiles) load_kv(kt + 1, (kt + 1) % STAGES);
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();  // tile kt (and Q) visible to all; everyone is done with the stage refilled below
+        if (kt + STAGES - 1 < num_tiles) load_kv(kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
         cp_async_commit();
+        compute_rows(kt + STAGES, (kt + STAGES) & 1);
 
         const int stage = kt % STAGES;
         const bf16* ks = Ks + stage * BN * LDS;
@@ -231,16 +261,29 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
 
         // mask, scale, running maximum
         float mx[2] = {-INFINITY, -INFINITY};
+        if (kw0 >= warp_lo_max && kw0 + KPW - 1 <= warp_pos_min && kw0 + KPW <= kend) {
+            // every key of this share is visible to every row of the warp
 #pragma unroll
-        for (int nt = 0; nt < KPW / 8; ++nt) {
+            for (int nt = 0; nt < KPW / 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = e >> 1;
-                const int j = kw0 + nt * 8 + 2 * tq + (e & 1);
-                const bool visible = j <= pos_r[i] && j >= lo_r[i] && j < kend;
-                const float v = visible ? s[nt][e] * p.scale_log2 : -INFINITY;
-                s[nt][e] = v;
-                mx[i] = fmaxf(mx[i], v);
+                for (int e = 0; e < 4; ++e) {
+                    const float v = s[nt][e] * p.scale_log2;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < KPW / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int j = kw0 + nt * 8 + 2 * tq + (e & 1);
+                    const bool visible = j <= pos_r[i] && j >= lo_r[i] && j < kend;
+                    const float v = visible ? s[nt][e] * p.scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    mx[i] = fmaxf(mx[i], v);
+                }
             }
         }
         float alpha[2], base[2];
@@ -362,7 +405,10 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
 
 // Combine the key ranges of decode-mode rows: one block per (token, head).
 template <int D>
-__global__ void attn_merge_kernel(const AttnParams p, const int* __restrict__ token_seg) {
+__global__ void attn_merge_kernel(const AttnParams p, const int* __restrict__ token_seg, const Prefetch pf) {
+    if (pi_prefetch_role(pf)) return;
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;  // token * nq + head
     const int t = row / p.nq;
     const int seg = token_seg[t];
@@ -386,16 +432,16 @@ __global__ void attn_merge_kernel(const AttnParams p, const int* __restrict__ to
     }
 }
 
-template <int ROW_WARPS, int KEY_WARPS>
+template <int ROW_WARPS, int KEY_WARPS, int STAGES>
 static size_t attn_smem_bytes() {
-    return (size_t)(ROW_WARPS * 16 + 2 * 2 * BN) * (PI_HEAD_DIM + 8) * sizeof(bf16);
+    return (size_t)(ROW_WARPS * 16 + 2 * STAGES * BN) * (PI_HEAD_DIM + 8) * sizeof(bf16);
 }
 
-template <int ROW_WARPS, int KEY_WARPS>
+template <int ROW_WARPS, int KEY_WARPS, int STAGES>
 static int launch_attn(const AttnParams& p, int num_segments, int splits, cudaStream_t stream) {
     static bool configured = false;  // once per process and kernel
-    const size_t smem = attn_smem_bytes<ROW_WARPS, KEY_WARPS>();
-    auto kernel = attn_mma_kernel<PI_HEAD_DIM, ROW_WARPS, KEY_WARPS>;
+    const size_t smem = attn_smem_bytes<ROW_WARPS, KEY_WARPS, STAGES>();
+    auto kernel = attn_mma_kernel<PI_HEAD_DIM, ROW_WARPS, KEY_WARPS, STAGES>;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) {
@@ -406,7 +452,7 @@ static int launch_attn(const AttnParams& p, int num_segments, int splits, cudaSt
         configured = true;
     }
     dim3 grid((unsigned)num_segments * p.tiles_per_seg, p.nkv, splits);
-    kernel<<<grid, ROW_WARPS * KEY_WARPS * 32, smem, stream>>>(p);
+    pi_launch(kernel, grid, dim3(ROW_WARPS * KEY_WARPS * 32), smem, stream, p);
     return pi_check_launch("pi_attention_mma");
 }
 
@@ -422,12 +468,15 @@ PI_EXPORT int pi_attention_num_splits(int pos, int window, int split_keys) {
 // has_prompt / has_decode say which kinds of segment the batch holds (a kernel is launched for each kind
 // present); max_seg_len bounds the grid of the prompt kernel; max_splits is the width of the scratch and the
 // grid depth of the decode kernel (>= the number of ranges of every decoding request in the batch).
-PI_EXPORT int pi_attention_mma(const void* q, int q_stride, const void* kcache, const void* vcache,
+// prefetch_ptr / prefetch_bytes: weights the next product will stream; the merge kernel's spare CTAs ask for them
+// to be brought into L2 (null / 0: none)
+PI_EXPORT int pi_attention_mma_prefetch(const void* q, int q_stride, const void* kcache, const void* vcache,
                                const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
                                const int* seg_start, const int* seg_len, const int* token_seg, void* out,
                                float* part_acc, float* part_ml, int max_splits, int split_keys, int num_tokens,
                                int num_segments, int max_seg_len, int has_prompt, int has_decode, int nq, int nkv,
-                               int page_size, int window, float scale, cudaStream_t stream) {
+                               int page_size, int window, float scale, const void* prefetch_ptr,
+                               unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (num_tokens <= 0 || num_segments <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return pi_refuse("pi_attention_mma: nq=%d must be a positive multiple of nkv=%d", nq, nkv);
     if (page_size <= 0) return pi_refuse("pi_attention_mma: page_size=%d must be positive", page_size);
@@ -445,10 +494,15 @@ PI_EXPORT int pi_attention_mma(const void* q, int q_stride, const void* kcache, 
     p.split_keys = split_keys;
     int rc = 0;
     if (has_prompt) {
-        constexpr int BM = 4 * 16;
         p.decode = 0;
-        p.tiles_per_seg = (int)(((long long)max_seg_len * p.group + BM - 1) / BM);
-        rc = launch_attn<4, 1>(p, num_segments, 1, stream);
+        const long long rows = (long long)max_seg_len * p.group;
+        if (rows > 64) {   // long portions: 128 rows per CTA halve the key/value traffic per query
+            p.tiles_per_seg = (int)((rows + 127) / 128);
+            rc = launch_attn<8, 1, 2>(p, num_segments, 1, stream);
+        } else {
+            p.tiles_per_seg = (int)((rows + 63) / 64);
+            rc = launch_attn<4, 1, 2>(p, num_segments, 1, stream);
+        }
         if (rc) return rc;
     }
     if (has_decode) {
@@ -456,14 +510,27 @@ PI_EXPORT int pi_attention_mma(const void* q, int q_stride, const void* kcache, 
         if (max_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return pi_refuse("pi_attention_mma: scratch for %d key ranges is missing", max_splits);
         p.decode = 1;
         p.tiles_per_seg = (p.group + 15) / 16;
-        rc = launch_attn<1, 4>(p, num_segments, max_splits, stream);
+        rc = launch_attn<1, 4, 3>(p, num_segments, max_splits, stream);
         if (rc) return rc;
         if (max_splits > 1) {
-            attn_merge_kernel<PI_HEAD_DIM><<<num_tokens * nq, PI_HEAD_DIM >= 128 ? 128 : 64, 0, stream>>>(p, token_seg);
+            const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, num_tokens * nq);
+            pi_launch(attn_merge_kernel<PI_HEAD_DIM>, dim3(num_tokens * nq + pi_prefetch_ctas(pf)), dim3(PI_HEAD_DIM >= 128 ? 128 : 64), 0, stream, p, token_seg, pf);
             rc = pi_check_launch("pi_attention_mma merge");
         }
     }
     return rc;
+}
+
+PI_EXPORT int pi_attention_mma(const void* q, int q_stride, const void* kcache, const void* vcache,
+                               const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                               const int* seg_start, const int* seg_len, const int* token_seg, void* out,
+                               float* part_acc, float* part_ml, int max_splits, int split_keys, int num_tokens,
+                               int num_segments, int max_seg_len, int has_prompt, int has_decode, int nq, int nkv,
+                               int page_size, int window, float scale, cudaStream_t stream) {
+    return pi_attention_mma_prefetch(q, q_stride, kcache, vcache, block_table, bt_stride, seg_off, seg_slot, seg_start,
+                                     seg_len, token_seg, out, part_acc, part_ml, max_splits, split_keys, num_tokens,
+                                     num_segments, max_seg_len, has_prompt, has_decode, nq, nkv, page_size, window, scale,
+                                     nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------

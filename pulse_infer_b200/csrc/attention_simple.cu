@@ -20,6 +20,8 @@ __global__ void attn_simple_kernel(const T* __restrict__ q, int q_stride, const 
                                    const int* __restrict__ token_slot, const int* __restrict__ positions,
                                    T* __restrict__ out, int nq, int nkv, int d, int page_size, int window, float scale) {
     extern __shared__ float qs_all[];  // [SIMPLE_WARPS][d]
+    pdl_wait();
+    pdl_trigger(PDL_ATTENTION);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * SIMPLE_WARPS + warp;
     if (head >= nq) return;  // whole warp leaves; no block-wide barrier below
@@ -97,11 +99,11 @@ PI_EXPORT int pi_attention_simple(const void* q, int q_stride, const void* kcach
     if (grid.y > 65535) return pi_refuse("pi_attention_simple: too many heads (%d)", nq);
     const size_t smem = (size_t)SIMPLE_WARPS * d * sizeof(float);
     if (dtype == PI_F32)
-        attn_simple_kernel<float><<<grid, SIMPLE_WARPS * 32, smem, stream>>>(
+        pi_launch(attn_simple_kernel<float>, grid, dim3(SIMPLE_WARPS * 32), smem, stream,
             (const float*)q, q_stride, (const float*)kcache, (const float*)vcache, block_table, bt_stride, token_slot,
             positions, (float*)out, nq, nkv, d, page_size, window, scale);
     else if (dtype == PI_BF16)
-        attn_simple_kernel<bf16><<<grid, SIMPLE_WARPS * 32, smem, stream>>>(
+        pi_launch(attn_simple_kernel<bf16>, grid, dim3(SIMPLE_WARPS * 32), smem, stream,
             (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride, token_slot,
             positions, (bf16*)out, nq, nkv, d, page_size, window, scale);
     else

@@ -26,6 +26,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC
 SOURCES = {
     "elementwise": "elementwise.cu",
     "gemm_f32": "gemm_f32.cu",
+    "gemm_small_m": "gemm_small_m.cu",
     "attention_simple": "attention_simple.cu",
     "sampling": "sampling.cu",
 }
@@ -65,19 +66,24 @@ def build_dir() -> str:
     raise BuildError(f"no writable build folder among {candidates}")
 
 
+def _extra_flags() -> list[str]:
+    """Extra nvcc flags from $PULSE_NVCC_FLAGS (experiments); they are part of the cache key."""
+    return os.environ.get("PULSE_NVCC_FLAGS", "").split()
+
+
 def _digest(source: str, defines: list[str]) -> str:
     h = hashlib.sha256()
     for name in [source] + HEADERS:
         with open(os.path.join(CSRC_DIR, name), "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + defines).encode())
+    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + defines + _extra_flags()).encode())
     return h.hexdigest()[:16]
 
 
 def _compile(source: str, out_path: str, defines: list[str], label: str) -> None:
     nvcc = find_nvcc()
     tmp_out = f"{out_path}.{os.getpid()}.tmp"
-    cmd = [nvcc] + ARCH_FLAGS + BASE_FLAGS + defines + ["-o", tmp_out, os.path.join(CSRC_DIR, source)]
+    cmd = [nvcc] + ARCH_FLAGS + BASE_FLAGS + defines + _extra_flags() + ["-o", tmp_out, os.path.join(CSRC_DIR, source)]
     print(f"[pulse_infer_b200] compiling {label} for sm_100a ...", file=sys.stderr, flush=True)
     t0 = time.time()
     env = dict(os.environ)

@@ -18,6 +18,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out,
                              int hidden, int vocab) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int id = tokens[t];
     const bool valid = id >= 0 && id < vocab;
@@ -32,9 +34,9 @@ PI_EXPORT int pi_embed(const int* tokens, const void* table, int table_dtype, fl
     if (hidden <= 0 || vocab <= 0) return pi_refuse("pi_embed: hidden=%d vocab=%d must be positive", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == PI_BF16)
-        embed_kernel<bf16><<<num_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, hidden, vocab);
+        pi_launch(embed_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, tokens, (const bf16*)table, out, hidden, vocab);
     else if (table_dtype == PI_F32)
-        embed_kernel<float><<<num_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
+        pi_launch(embed_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, hidden, vocab);
     else
         return pi_refuse("pi_embed: unknown table dtype code %d", table_dtype);
     return pi_check_launch("pi_embed");
@@ -48,8 +50,12 @@ PI_EXPORT int pi_embed(const int* tokens, const void* table, int table_dtype, fl
 // ---------------------------------------------------------------------------------------------------
 template <typename TA, typename TW, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__ delta, const TW* __restrict__ w,
-                                   TA* __restrict__ x, const int* __restrict__ rows, int hidden, float eps) {
+                                   TA* __restrict__ x, const int* __restrict__ rows, int hidden, float eps,
+                                   const Prefetch pf) {
     __shared__ float scratch[33];
+    if (pi_prefetch_role(pf)) return;
+    pdl_wait();
+    pdl_trigger();
     const int out_row = blockIdx.x;
     const int src_row = rows ? rows[out_row] : out_row;
     float* hr = h + (size_t)src_row * hidden;
@@ -97,24 +103,94 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
     }
 }
 
+// Same operation with the row held in registers: every load (residual, delta, weight) is issued before
+// anything is computed, so a row costs one trip to memory instead of three.  Needs hidden % 4 == 0 and
+// hidden <= 256 * 4 * ITEMS.
+template <typename TA, typename TW, int ITEMS>
+__global__ void __launch_bounds__(256) add_rmsnorm_reg_kernel(float* __restrict__ h, const TA* __restrict__ delta,
+                                                              const TW* __restrict__ w, TA* __restrict__ x,
+                                                              const int* __restrict__ rows, int hidden, float eps,
+                                                              const Prefetch pf) {
+    __shared__ float scratch[33];
+    struct alignas(sizeof(TA) * 4) PackA { TA v[4]; };
+    struct alignas(sizeof(TW) * 4) PackW { TW v[4]; };
+    if (pi_prefetch_role(pf)) return;
+    pdl_wait();
+    pdl_trigger();
+    const int out_row = blockIdx.x;
+    const int src_row = rows ? rows[out_row] : out_row;
+    float* hr = h + (size_t)src_row * hidden;
+    const TA* dr = delta ? delta + (size_t)src_row * hidden : nullptr;
+    TA* xr = x + (size_t)out_row * hidden;
+    const bool store_h = (rows == nullptr) && (delta != nullptr);
+
+    float4 hv[ITEMS];
+    PackA dv[ITEMS];
+    PackW wv[ITEMS];
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int i = (it * 256 + threadIdx.x) * 4;
+        if (i < hidden) {
+            hv[it] = *reinterpret_cast<const float4*>(hr + i);
+            if (dr) dv[it] = *reinterpret_cast<const PackA*>(dr + i);
+            wv[it] = *reinterpret_cast<const PackW*>(w + i);
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int i = (it * 256 + threadIdx.x) * 4;
+        if (i < hidden) {
+            if (dr) {
+                hv[it].x += to_float<TA>(dv[it].v[0]); hv[it].y += to_float<TA>(dv[it].v[1]);
+                hv[it].z += to_float<TA>(dv[it].v[2]); hv[it].w += to_float<TA>(dv[it].v[3]);
+            }
+            ss += hv[it].x * hv[it].x + hv[it].y * hv[it].y + hv[it].z * hv[it].z + hv[it].w * hv[it].w;
+            if (store_h) *reinterpret_cast<float4*>(hr + i) = hv[it];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int i = (it * 256 + threadIdx.x) * 4;
+        if (i < hidden) {
+            PackA o;
+            o.v[0] = from_float<TA>(hv[it].x * inv * to_float<TW>(wv[it].v[0]));
+            o.v[1] = from_float<TA>(hv[it].y * inv * to_float<TW>(wv[it].v[1]));
+            o.v[2] = from_float<TA>(hv[it].z * inv * to_float<TW>(wv[it].v[2]));
+            o.v[3] = from_float<TA>(hv[it].w * inv * to_float<TW>(wv[it].v[3]));
+            *reinterpret_cast<PackA*>(xr + i) = o;
+        }
+    }
+}
+
 template <typename TA, typename TW>
 static void launch_add_rmsnorm(float* h, const void* delta, const void* w, void* x, const int* rows, int n, int hidden,
-                               float eps, cudaStream_t stream) {
+                               float eps, const Prefetch pf, cudaStream_t stream) {
     const int threads = hidden >= 2048 ? 256 : 128;
-    if (hidden % 4 == 0)
-        add_rmsnorm_kernel<TA, TW, 4><<<n, threads, 0, stream>>>(h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps);
+    if (hidden % 4 == 0 && hidden <= 256 * 4 * 2)
+        pi_launch(add_rmsnorm_reg_kernel<TA, TW, 2>, dim3(n + pi_prefetch_ctas(pf)), dim3(256), 0, stream, h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps, pf);
+    else if (hidden % 4 == 0 && hidden <= 256 * 4 * 4)
+        pi_launch(add_rmsnorm_reg_kernel<TA, TW, 4>, dim3(n + pi_prefetch_ctas(pf)), dim3(256), 0, stream, h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps, pf);
+    else if (hidden % 4 == 0 && hidden <= 256 * 4 * 8)
+        pi_launch(add_rmsnorm_reg_kernel<TA, TW, 8>, dim3(n + pi_prefetch_ctas(pf)), dim3(256), 0, stream, h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps, pf);
+    else if (hidden % 4 == 0)
+        pi_launch(add_rmsnorm_kernel<TA, TW, 4>, dim3(n + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps, pf);
     else
-        add_rmsnorm_kernel<TA, TW, 1><<<n, threads, 0, stream>>>(h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps);
+        pi_launch(add_rmsnorm_kernel<TA, TW, 1>, dim3(n + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, h, (const TA*)delta, (const TW*)w, (TA*)x, rows, hidden, eps, pf);
 }
 
 PI_EXPORT int pi_add_rmsnorm(float* h, const void* delta, const void* weight, int weight_dtype, void* x, int act_dtype,
-                             const int* rows, int n, int hidden, float eps, cudaStream_t stream) {
+                             const int* rows, int n, int hidden, float eps, const void* prefetch_ptr,
+                             unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (hidden <= 0) return pi_refuse("pi_add_rmsnorm: hidden=%d must be positive", hidden);
-    if (act_dtype == PI_BF16 && weight_dtype == PI_BF16) launch_add_rmsnorm<bf16, bf16>(h, delta, weight, x, rows, n, hidden, eps, stream);
-    else if (act_dtype == PI_BF16 && weight_dtype == PI_F32) launch_add_rmsnorm<bf16, float>(h, delta, weight, x, rows, n, hidden, eps, stream);
-    else if (act_dtype == PI_F32 && weight_dtype == PI_F32) launch_add_rmsnorm<float, float>(h, delta, weight, x, rows, n, hidden, eps, stream);
-    else if (act_dtype == PI_F32 && weight_dtype == PI_BF16) launch_add_rmsnorm<float, bf16>(h, delta, weight, x, rows, n, hidden, eps, stream);
+    const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, n);
+    if (act_dtype == PI_BF16 && weight_dtype == PI_BF16) launch_add_rmsnorm<bf16, bf16>(h, delta, weight, x, rows, n, hidden, eps, pf, stream);
+    else if (act_dtype == PI_BF16 && weight_dtype == PI_F32) launch_add_rmsnorm<bf16, float>(h, delta, weight, x, rows, n, hidden, eps, pf, stream);
+    else if (act_dtype == PI_F32 && weight_dtype == PI_F32) launch_add_rmsnorm<float, float>(h, delta, weight, x, rows, n, hidden, eps, pf, stream);
+    else if (act_dtype == PI_F32 && weight_dtype == PI_BF16) launch_add_rmsnorm<float, bf16>(h, delta, weight, x, rows, n, hidden, eps, pf, stream);
     else return pi_refuse("pi_add_rmsnorm: unknown dtype codes act=%d weight=%d", act_dtype, weight_dtype);
     return pi_check_launch("pi_add_rmsnorm");
 }
@@ -123,7 +199,10 @@ PI_EXPORT int pi_add_rmsnorm(float* h, const void* delta, const void* weight, in
 // SiLU(gate) * up on the fused [n, 2*inter] output of the gate_up product: out[n, inter]
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, const Prefetch pf) {
+    if (pi_prefetch_role(pf)) return;
+    pdl_wait();
+    pdl_trigger();
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= total) return;
     const size_t row = e / inter;
@@ -135,8 +214,12 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 
 // 8 elements (bf16) or 4 (float) per thread with 16-byte accesses; needs inter % VEC == 0
 template <typename T, int VEC>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs,
+                                    const Prefetch pf) {
     struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+    if (pi_prefetch_role(pf)) return;
+    pdl_wait();
+    pdl_trigger();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total_vecs) return;
     const int vecs_per_row = inter / VEC;
@@ -153,24 +236,30 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
     *reinterpret_cast<Pack*>(out + row * (size_t)inter + col) = o;
 }
 
-PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, cudaStream_t stream) {
+PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, const void* prefetch_ptr,
+                          unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (inter <= 0) return pi_refuse("pi_silu_mul: inter=%d must be positive", inter);
     const size_t total = (size_t)n * inter;
     const int threads = 256;
     if (dtype == PI_BF16 && inter % 8 == 0) {
         const size_t vecs = total / 8;
-        silu_mul_vec_kernel<bf16, 8><<<(unsigned)((vecs + threads - 1) / threads), threads, 0, stream>>>(
-            (const bf16*)gate_up, (bf16*)out, inter, vecs);
+        const unsigned own = (unsigned)((vecs + threads - 1) / threads);
+        const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, (int)own);
+        pi_launch(silu_mul_vec_kernel<bf16, 8>, dim3(own + pi_prefetch_ctas(pf)), dim3(threads), 0, stream,
+                  (const bf16*)gate_up, (bf16*)out, inter, vecs, pf);
     } else if (dtype == PI_F32 && inter % 4 == 0) {
         const size_t vecs = total / 4;
-        silu_mul_vec_kernel<float, 4><<<(unsigned)((vecs + threads - 1) / threads), threads, 0, stream>>>(
-            (const float*)gate_up, (float*)out, inter, vecs);
+        const unsigned own = (unsigned)((vecs + threads - 1) / threads);
+        const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, (int)own);
+        pi_launch(silu_mul_vec_kernel<float, 4>, dim3(own + pi_prefetch_ctas(pf)), dim3(threads), 0, stream,
+                  (const float*)gate_up, (float*)out, inter, vecs, pf);
     } else if (dtype == PI_BF16 || dtype == PI_F32) {
         // widths that are no multiple of the vector: rows may start unaligned, so plain element accesses
         const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-        if (dtype == PI_BF16) silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
-        else silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+        const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, (int)blocks);
+        if (dtype == PI_BF16) pi_launch(silu_mul_kernel<bf16>, dim3(blocks + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total, pf);
+        else pi_launch(silu_mul_kernel<float>, dim3(blocks + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total, pf);
     } else {
         return pi_refuse("pi_silu_mul: unknown dtype code %d", dtype);
     }
@@ -182,6 +271,8 @@ PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int 
 // ---------------------------------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ divisors,
                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int num_tokens, int pairs) {
+    pdl_wait();
+    pdl_trigger();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= num_tokens * pairs) return;
     const int t = idx / pairs, i = idx % pairs;
@@ -196,8 +287,8 @@ PI_EXPORT int pi_rope_table(const int* positions, const double* divisors, float*
                             int pairs, cudaStream_t stream) {
     if (num_tokens <= 0 || pairs <= 0) return 0;
     const int total = num_tokens * pairs, threads = 128;
-    rope_table_kernel<<<(total + threads - 1) / threads, threads, 0, stream>>>(positions, divisors, cos_out, sin_out,
-                                                                               num_tokens, pairs);
+    pi_launch(rope_table_kernel, dim3((total + threads - 1) / threads), dim3(threads), 0, stream, positions, divisors, cos_out,
+              sin_out, num_tokens, pairs);
     return pi_check_launch("pi_rope_table");
 }
 
@@ -221,7 +312,11 @@ __global__ void qk_norm_rope_write_kernel(TA* __restrict__ qkv, int row_stride, 
                                           int adjacent, TA* __restrict__ kcache, TA* __restrict__ vcache,
                                           const int* __restrict__ block_table, int bt_stride,
                                           const int* __restrict__ token_slot, const int* __restrict__ positions,
-                                          int page_size, int nq, int nkv, int d, int* __restrict__ error_count) {
+                                          int page_size, int nq, int nkv, int d, int* __restrict__ error_count,
+                                          const Prefetch pf) {
+    if (pi_prefetch_role(pf)) return;
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -298,7 +393,8 @@ PI_EXPORT int pi_qk_norm_rope_write(void* qkv, int row_stride, int act_dtype, co
                                     int weight_dtype, float eps, int has_norm, const float* cos_t, const float* sin_t,
                                     int rot_pairs, int adjacent, void* kcache, void* vcache, const int* block_table,
                                     int bt_stride, const int* token_slot, const int* positions, int page_size, int nq,
-                                    int nkv, int d, int num_tokens, int* error_count, cudaStream_t stream) {
+                                    int nkv, int d, int num_tokens, int* error_count, const void* prefetch_ptr,
+                                    unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (d <= 0 || d % 2 != 0 || d > 64 * QK_MAX_PAIRS)
         return pi_refuse("pi_qk_norm_rope_write: head_dim=%d must be even and at most %d", d, 64 * QK_MAX_PAIRS);
@@ -306,11 +402,12 @@ PI_EXPORT int pi_qk_norm_rope_write(void* qkv, int row_stride, int act_dtype, co
     if (nq < 0 || nkv < 0 || nq + nkv == 0) return pi_refuse("pi_qk_norm_rope_write: nq=%d nkv=%d", nq, nkv);
     if (nkv > 0 && page_size <= 0) return pi_refuse("pi_qk_norm_rope_write: page_size=%d must be positive", page_size);
     const int warps = 4;
-    dim3 grid(num_tokens, (nq + 2 * nkv + warps - 1) / warps);
+    const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, num_tokens);
+    dim3 grid(num_tokens + pi_prefetch_ctas(pf), (nq + 2 * nkv + warps - 1) / warps);
 #define QK_LAUNCH(TA, TW)                                                                                              \
-    qk_norm_rope_write_kernel<TA, TW><<<grid, warps * 32, 0, stream>>>(                                                 \
+    pi_launch(qk_norm_rope_write_kernel<TA, TW>, grid, dim3(warps * 32), 0, stream,                                      \
         (TA*)qkv, row_stride, (const TW*)q_weight, (const TW*)k_weight, eps, has_norm, cos_t, sin_t, rot_pairs, adjacent, \
-        (TA*)kcache, (TA*)vcache, block_table, bt_stride, token_slot, positions, page_size, nq, nkv, d, error_count)
+        (TA*)kcache, (TA*)vcache, block_table, bt_stride, token_slot, positions, page_size, nq, nkv, d, error_count, pf)
     if (act_dtype == PI_BF16 && weight_dtype == PI_BF16) QK_LAUNCH(bf16, bf16);
     else if (act_dtype == PI_BF16 && weight_dtype == PI_F32) QK_LAUNCH(bf16, float);
     else if (act_dtype == PI_F32 && weight_dtype == PI_F32) QK_LAUNCH(float, float);

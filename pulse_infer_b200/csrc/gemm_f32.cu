@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(256) gemm_f32_nt_kernel(const float* __restric
                                                           int ldc, int M, int N, int K) {
     __shared__ float As[TILE_K][TILE_M + 4];
     __shared__ float Ws[TILE_K][TILE_N + 4];
+    pdl_wait();
+    pdl_trigger(PDL_PRODUCT);
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;  // 16 x 16 threads, each a 4 x 4 patch
     const int m0 = blockIdx.y * TILE_M, n0 = blockIdx.x * TILE_N;
@@ -70,6 +72,6 @@ PI_EXPORT int pi_gemm_f32_nt(const float* A, int lda, const float* W, int ldw, f
     if (lda < K || ldw < K || ldc < N) return pi_refuse("pi_gemm_f32_nt: leading dimensions (%d, %d, %d) too small", lda, ldw, ldc);
     dim3 grid((N + TILE_N - 1) / TILE_N, (M + TILE_M - 1) / TILE_M);
     if (grid.y > 65535) return pi_refuse("pi_gemm_f32_nt: M=%d is beyond the grid limit", M);
-    gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
+    pi_launch(gemm_f32_nt_kernel, grid, dim3(256), 0, stream, A, lda, W, ldw, C, ldc, M, N, K);
     return pi_check_launch("pi_gemm_f32_nt");
 }

@@ -1,0 +1,145 @@
+// Weight-streaming matrix product for decoding: out[M, N] = x[M, K] * W[N, K]^T in bfloat16 with 32-bit
+// accumulation, for a handful of rows (M <= 32).  Every weight is read exactly once, in 16-byte pieces
+// that bypass L1, and the product runs on tensor cores with the roles swapped: 16 rows of W are the
+// 16-row operand of mma.sync m16n8k16 and 8 rows of x (8 requests) are its 8 columns, so nothing is
+// padded along the batch.  The few hundred kilobytes of x stay in L1/L2.
+//
+// A CTA owns 16 output features; its warps split K into contiguous ranges and their partial sums are added
+// in warp order through shared memory, so a result does not depend on the launch or on the other rows.
+// (Splitting K further across the CTAs of a thread-block cluster, reduced through distributed shared memory,
+// was measured and dropped: it made the 33-100 MB products of a decode step slower, not faster.)
+//
+// Within a 32-wide block of k, thread t of a quad supplies elements 8t..8t+7 of its row for both operands:
+// 8t+0..3 go to the four k slots that the thread owns in the first mma, 8t+4..7 to those of the second.  The
+// sum over k does not care which element sits in which slot as long as both operands agree.
+//
+// Reference parity: the reference calls cublasGemmEx for every product, also at one row
+// (src/ops/kernels/cuda/matmul_kernel.cu:132-154); weights are [out, in] and used transposed
+// (src/layer/linear.cpp:213).
+#include "common.cuh"
+
+#define SM_WARPS 8          // warps per CTA, each takes 1/8 of K
+#define SM_FEATURES 16      // output features per CTA
+#define SM_UNROLL 4         // k blocks in flight per warp
+
+__device__ __forceinline__ uint4 ld_stream16(const void* ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                          unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT, typename TO>   // MT: tiles of 8 rows of x
+__global__ void __launch_bounds__(SM_WARPS * 32) gemm_small_m_kernel(const bf16* __restrict__ x, int ldx,
+                                                                     const bf16* __restrict__ W, int ldw,
+                                                                     TO* __restrict__ out, int ldo, int M, int N, int K) {
+    __shared__ float partial[SM_WARPS][SM_FEATURES][MT * 8 + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * SM_FEATURES;
+
+    // rows of W this thread reads (clamped: rows beyond N are computed and dropped)
+    const int ra = min(n0 + g, N - 1), rb = min(n0 + g + 8, N - 1);
+    const bf16* wa = W + (size_t)ra * ldw + 8 * t;
+    const bf16* wb = W + (size_t)rb * ldw + 8 * t;
+    const bf16* xr[MT];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) xr[i] = x + (size_t)min(8 * i + g, M - 1) * ldx + 8 * t;
+
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
+
+    // 32-wide blocks of k, one contiguous range per warp
+    const int blocks = (K + 31) / 32;
+    const int per_warp = (blocks + SM_WARPS - 1) / SM_WARPS;
+    const int b_begin = warp * per_warp, b_end = min(blocks, b_begin + per_warp);
+
+    // Two register sets of SM_UNROLL blocks each: while one is multiplied the other is in flight.  The first
+    // set is requested before pdl_wait(): weights do not depend on the kernel that produces x.
+    uint4 va0[SM_UNROLL], vb0[SM_UNROLL], va1[SM_UNROLL], vb1[SM_UNROLL];
+    auto load_w = [&](int b, uint4 (&va)[SM_UNROLL], uint4 (&vb)[SM_UNROLL]) {
+#pragma unroll
+        for (int u = 0; u < SM_UNROLL; ++u) {
+            const int k = (b + u) * 32 + 8 * t;
+            const bool valid = (b + u) < b_end && k + 8 <= K;
+            va[u] = valid ? ld_stream16(wa + (size_t)(b + u) * 32) : make_uint4(0, 0, 0, 0);
+            vb[u] = valid ? ld_stream16(wb + (size_t)(b + u) * 32) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto multiply = [&](int b, const uint4 (&va)[SM_UNROLL], const uint4 (&vb)[SM_UNROLL]) {
+#pragma unroll
+        for (int u = 0; u < SM_UNROLL; ++u) {
+            const int k = (b + u) * 32 + 8 * t;
+            const bool valid = (b + u) < b_end && k + 8 <= K;
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                const uint4 xv = valid ? __ldg(reinterpret_cast<const uint4*>(xr[i] + (size_t)(b + u) * 32))
+                                       : make_uint4(0, 0, 0, 0);
+                mma_16816(acc[i], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
+                mma_16816(acc[i], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
+            }
+        }
+    };
+    load_w(b_begin, va0, vb0);
+    pdl_wait();
+    pdl_trigger(PDL_PRODUCT);
+    for (int b = b_begin; b < b_end; b += 2 * SM_UNROLL) {
+        load_w(b + SM_UNROLL, va1, vb1);
+        multiply(b, va0, vb0);
+        load_w(b + 2 * SM_UNROLL, va0, vb0);
+        multiply(b + SM_UNROLL, va1, vb1);
+    }
+
+    // acc[i][0..1]: feature g, rows 8i + 2t, 8i + 2t + 1;  acc[i][2..3]: feature g + 8, same rows
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+        partial[warp][g][8 * i + 2 * t] = acc[i][0];
+        partial[warp][g][8 * i + 2 * t + 1] = acc[i][1];
+        partial[warp][g + 8][8 * i + 2 * t] = acc[i][2];
+        partial[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < SM_FEATURES * MT * 8; idx += SM_WARPS * 32) {
+        const int m = idx / SM_FEATURES, f = idx % SM_FEATURES;   // neighbouring threads take neighbouring features
+        if (m >= M || n0 + f >= N) continue;
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SM_WARPS; ++w) sum += partial[w][f][m];
+        out[(size_t)m * ldo + n0 + f] = from_float<TO>(sum);
+    }
+}
+
+template <int MT>
+static void launch_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                           int K, cudaStream_t stream) {
+    const dim3 grid((unsigned)((N + SM_FEATURES - 1) / SM_FEATURES));
+    if (out_dtype == PI_F32)
+        pi_launch(gemm_small_m_kernel<MT, float>, grid, dim3(SM_WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (float*)out, ldo, M, N, K);
+    else
+        pi_launch(gemm_small_m_kernel<MT, bf16>, grid, dim3(SM_WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K);
+}
+
+PI_EXPORT int pi_gemm_small_m_max_rows() { return 32; }
+
+PI_EXPORT int pi_gemm_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                              int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 32) return pi_refuse("pi_gemm_small_m: %d rows; this kernel takes at most 32", M);
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
+        return pi_refuse("pi_gemm_small_m: K=%d and the leading dimensions (%d, %d) must be positive multiples of 8", K, ldx, ldw);
+    if (ldx < K || ldw < K || ldo < N) return pi_refuse("pi_gemm_small_m: leading dimensions (%d, %d, %d) too small", ldx, ldw, ldo);
+    if (((uintptr_t)x | (uintptr_t)W) & 15) return pi_refuse("pi_gemm_small_m: operands must be 16-byte aligned");
+    if (out_dtype != PI_F32 && out_dtype != PI_BF16) return pi_refuse("pi_gemm_small_m: unknown output dtype code %d", out_dtype);
+    if (M <= 8) launch_small_m<1>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream);
+    else if (M <= 16) launch_small_m<2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream);
+    else launch_small_m<4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream);
+    return pi_check_launch("pi_gemm_small_m");
+}

@@ -80,14 +80,70 @@ __device__ ArgMax block_argmax(const float* __restrict__ x, int n, ArgMax* sh /*
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
     __shared__ ArgMax sh[33];
+    pdl_wait();
+    pdl_trigger();
     const ArgMax r = block_argmax(logits + (size_t)blockIdx.x * ld, vocab, sh);
     if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
 
-PI_EXPORT int pi_argmax(const float* logits, int ld, int rows, int vocab, int* out, cudaStream_t stream) {
+// Large vocabularies: a row is cut into slices scanned by separate blocks (one block per row would leave
+// most of the GPU idle and take tens of microseconds), then one small block per row picks among the slices.
+#define ARGMAX_SLICE 4096
+__global__ void argmax_slices_kernel(const float* __restrict__ logits, int ld, int vocab, float* __restrict__ cand_val,
+                                     int* __restrict__ cand_idx, int slices) {
+    __shared__ ArgMax sh[33];
+    pdl_wait();
+    pdl_trigger();
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const int begin = slice * ARGMAX_SLICE;
+    const int n = min(ARGMAX_SLICE, vocab - begin);
+    ArgMax r = block_argmax(logits + (size_t)row * ld + begin, n, sh);
+    if (threadIdx.x == 0) {
+        cand_val[row * slices + slice] = r.v;
+        cand_idx[row * slices + slice] = r.i < 0 ? -1 : r.i + begin;
+    }
+}
+
+__global__ void argmax_pick_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_idx, int slices,
+                                   int* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
+    const int row = blockIdx.x;
+    ArgMax best = {-INFINITY, -1};
+    for (int i = threadIdx.x; i < slices; i += 32) {   // ascending index per lane; ties keep the lower index
+        ArgMax c = {cand_val[row * slices + i], cand_idx[row * slices + i]};
+        best = better(best, c);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax other;
+        other.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+        best = better(best, other);
+    }
+    if (threadIdx.x == 0) out[row] = best.i;
+}
+
+PI_EXPORT int pi_argmax_scratch_floats(int rows, int vocab) {
+    const int slices = (vocab + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
+    return vocab >= 4 * ARGMAX_SLICE ? 2 * rows * slices : 0;
+}
+
+// scratch: pi_argmax_scratch_floats(rows, vocab) 4-byte words (may be null when that is 0)
+PI_EXPORT int pi_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* scratch, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || ld < vocab) return pi_refuse("pi_argmax: vocab=%d ld=%d", vocab, ld);
-    argmax_kernel<<<rows, vocab >= 4096 ? 1024 : 256, 0, stream>>>(logits, ld, vocab, out);
+    if (vocab >= 4 * ARGMAX_SLICE) {
+        if (scratch == nullptr) return pi_refuse("pi_argmax: scratch is missing");
+        if (rows > 65535) return pi_refuse("pi_argmax: %d rows are beyond the grid limit", rows);
+        const int slices = (vocab + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
+        float* cand_val = (float*)scratch;
+        int* cand_idx = (int*)scratch + (size_t)rows * slices;
+        pi_launch(argmax_slices_kernel, dim3(slices, rows), dim3(256), 0, stream, logits, ld, vocab, cand_val, cand_idx, slices);
+        pi_launch(argmax_pick_kernel, dim3(rows), dim3(32), 0, stream, (const float*)cand_val, (const int*)cand_idx, slices, out);
+    } else {
+        pi_launch(argmax_kernel, dim3(rows), dim3(vocab >= 4096 ? 1024 : 256), 0, stream, logits, ld, vocab, out);
+    }
     return pi_check_launch("pi_argmax");
 }
 
@@ -129,6 +185,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int voca
     __shared__ float sh_f[33];
     __shared__ int sh_i[33];
     __shared__ int sh_pick;
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;
     const float* x = logits + (size_t)row * ld;
     const ArgMax top = block_argmax(x, vocab, sh_arg);
@@ -239,14 +297,16 @@ PI_EXPORT int pi_sample(const float* logits, int ld, int rows, int vocab, const 
     if (rows <= 0) return 0;
     if (vocab <= 0 || ld < vocab) return pi_refuse("pi_sample: vocab=%d ld=%d", vocab, ld);
     if (vocab > (1 << 24)) return pi_refuse("pi_sample: vocab=%d is beyond 2^24", vocab);
-    sample_kernel<<<rows, vocab >= 4096 ? 1024 : 256, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p, seeds,
-                                                                    counters, out);
+    pi_launch(sample_kernel, dim3(rows), dim3(vocab >= 4096 ? 1024 : 256), 0, stream, logits, ld, vocab, temperature, top_k,
+              top_p, seeds, counters, out);
     return pi_check_launch("pi_sample");
 }
 
 // logits[rows[i], tokens[i]] = set ? values[i] : logits[...] + values[i]; (row, token) pairs must be distinct
 __global__ void logit_edit_kernel(float* __restrict__ logits, int ld, int vocab, const int* __restrict__ rows,
                                   const int* __restrict__ tokens, const float* __restrict__ values, int n, int set) {
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int tok = tokens[i];
@@ -258,6 +318,6 @@ __global__ void logit_edit_kernel(float* __restrict__ logits, int ld, int vocab,
 PI_EXPORT int pi_logit_edit(float* logits, int ld, int vocab, const int* rows, const int* tokens, const float* values,
                             int n, int set, cudaStream_t stream) {
     if (n <= 0) return 0;
-    logit_edit_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, ld, vocab, rows, tokens, values, n, set);
+    pi_launch(logit_edit_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, logits, ld, vocab, rows, tokens, values, n, set);
     return pi_check_launch("pi_logit_edit");
 }

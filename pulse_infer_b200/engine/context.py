@@ -12,6 +12,7 @@ into tokens / positions / seq ids; the reference then uploads a block table with
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -47,6 +48,7 @@ class AttentionScratch:
     max_splits: int
     acc: torch.Tensor | None
     ml: torch.Tensor | None
+    split_keys: int = ops.SPLIT_KEYS
 
 
 class StepContext:
@@ -65,7 +67,12 @@ class StepContext:
         self.segments: list = []
         self._scratch: dict = {}
         self.splits_bound: int | None = None     # fixed number of key ranges (captured steps)
+        self.split_keys: int | None = None       # fixed keys per range (captured steps); else chosen per step
         self.error_count: torch.Tensor | None = None
+        self.upcoming_weights = None
+        self.prefetch_hints = os.environ.get("PULSE_PREFETCH", "1") != "0"
+        self.prefetch_bytes = int(float(os.environ.get("PULSE_PREFETCH_MB", "4")) * (1 << 20))
+        self.num_tokens = 0
 
     # ---- layout of the metadata buffer -------------------------------------------------------------
     @staticmethod
@@ -137,6 +144,19 @@ class StepContext:
         self.decode_pos_max = max([s.start for s in segments if len(s.tokens) == 1], default=0)
         self._scratch = {}
 
+    # ---- prefetch hints --------------------------------------------------------------------------------
+    PREFETCH_MAX_TOKENS = 16      # only steps this small stream their weights once (decode); others reuse them
+
+    def prefetch(self, weights):
+        """The tensor to hand to a small kernel as "the next product's weights", or None when a hint would
+        not help (large steps, float32 path, hints switched off)."""
+        if weights is None or not self.prefetch_hints or self.num_tokens > self.PREFETCH_MAX_TOKENS:
+            return None
+        if weights.dtype != torch.bfloat16 or not weights.is_cuda:
+            return None
+        limit = self.prefetch_bytes // weights.element_size()
+        return weights if weights.numel() <= limit else weights.reshape(-1)[:limit]
+
     # ---- what parts ask for --------------------------------------------------------------------------
     def cache_view(self, cache_index, layer_index) -> CacheView:
         cm = self.cache_manager
@@ -147,7 +167,7 @@ class StepContext:
         keys, values = group.kv(cache_index)
         return CacheView(keys, values, group.device_table, cm.page_size, state)
 
-    def attention_scratch(self, num_heads: int, head_dim: int, window) -> AttentionScratch:
+    def attention_scratch(self, num_heads: int, head_dim: int, window, num_kv_heads: int = 1) -> AttentionScratch:
         """Scratch of the split decode attention: partial outputs and (max, sum) pairs per key range."""
         key = (num_heads, head_dim, window)
         sc = self._scratch.get(key)
@@ -155,13 +175,15 @@ class StepContext:
             if not self.has_decode:
                 sc = AttentionScratch(1, None, None)
             else:
-                splits = self.splits_bound or ops.attention_num_splits(self.decode_pos_max, window)
+                num_decode = sum(1 for s in self.segments if len(s.tokens) == 1)
+                split_keys = self.split_keys or ops.choose_split_keys(num_decode, num_kv_heads, self.decode_pos_max)
+                splits = self.splits_bound or ops.attention_num_splits(self.decode_pos_max, window, split_keys)
                 if splits > 1:
                     rows = self.num_tokens * num_heads
                     acc = torch.empty((rows, splits, head_dim), dtype=torch.float32, device=self.device)
                     ml = torch.empty((rows, splits, 2), dtype=torch.float32, device=self.device)
-                    sc = AttentionScratch(splits, acc, ml)
+                    sc = AttentionScratch(splits, acc, ml, split_keys)
                 else:
-                    sc = AttentionScratch(1, None, None)
+                    sc = AttentionScratch(1, None, None, split_keys)
             self._scratch[key] = sc
         return sc

@@ -23,7 +23,7 @@ def _pow2_at_least(n: int) -> int:
 
 
 class DecodeGraph:
-    def __init__(self, runner, num_requests: int, splits_bound: int):
+    def __init__(self, runner, num_requests: int, split_keys: int, splits_bound: int):
         self.runner = runner
         self.num_requests = num_requests
         self.splits_bound = splits_bound
@@ -38,6 +38,7 @@ class DecodeGraph:
         self.ctx.buffer = torch.zeros(total, dtype=torch.int32, device=device)
         self.ctx.error_count = torch.zeros(1, dtype=torch.int32, device=device)
         self.ctx.splits_bound = splits_bound
+        self.ctx.split_keys = split_keys
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
 
@@ -84,14 +85,16 @@ class DecodeGraphs:
         return all(len(s.tokens) == 1 and list(s.want) == [0] for s in segments)
 
     def run(self, segments) -> torch.Tensor:
-        windows = {cs.window for cs in self.runner.model.cache_specs() if cs is not None}
+        specs = [cs for cs in self.runner.model.cache_specs() if cs is not None]
+        windows = {cs.window for cs in specs}
         pos_max = max(s.start for s in segments)
-        need = max(ops.attention_num_splits(pos_max, w) for w in windows) if windows else 1
-        key = (len(segments), _pow2_at_least(need))
+        split_keys = ops.choose_split_keys(len(segments), max((cs.num_kv_heads for cs in specs), default=1), pos_max)
+        need = max(ops.attention_num_splits(pos_max, w, split_keys) for w in windows) if windows else 1
+        key = (len(segments), split_keys, _pow2_at_least(need))
         g = self.graphs.get(key)
         if g is None:
             if len(self.graphs) >= self.max_graphs:
                 self.graphs.pop(next(iter(self.graphs)))
-            g = DecodeGraph(self.runner, key[0], key[1])
+            g = DecodeGraph(self.runner, *key)
             self.graphs[key] = g
         return g.run(segments)

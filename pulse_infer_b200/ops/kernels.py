@@ -65,6 +65,13 @@ def _p(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+def _prefetch_args(t: torch.Tensor | None):
+    """(pointer, bytes) of weights that small kernels may ask the L2 to fetch ahead of the next product."""
+    if t is None:
+        return c_void_p(0), ctypes.c_ulonglong(0)
+    return c_void_p(t.data_ptr()), ctypes.c_ulonglong(t.numel() * t.element_size())
+
+
 def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -111,7 +118,8 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = 
 
 # ---- fused residual add + RMSNorm ---------------------------------------------------------------------
 def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
-                out_dtype: torch.dtype, rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                out_dtype: torch.dtype, rows: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                prefetch: torch.Tensor | None = None) -> torch.Tensor:
     """hidden fp32 [T, H].  Without ``rows``: hidden += delta in place and the norm of every row is
     returned.  With ``rows`` (int32 [n]): the norm of hidden[rows] + delta[rows]; hidden is not changed."""
     _need_cuda(hidden, delta, weight, rows)
@@ -130,13 +138,13 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
         out = torch.empty((n, H), dtype=out_dtype, device=hidden.device)
     lib = _lib("elementwise")
     _check(lib, lib.pi_add_rmsnorm(_p(hidden), _p(delta), _p(weight), c_int(_code(weight.dtype)), _p(out),
-                                   c_int(_code(out_dtype)), _p(rows), c_int(n), c_int(H), c_float(eps), _stream()),
-           "add_rmsnorm")
+                                   c_int(_code(out_dtype)), _p(rows), c_int(n), c_int(H), c_float(eps),
+                                   *_prefetch_args(prefetch), _stream()), "add_rmsnorm")
     return out
 
 
 # ---- SiLU(gate) * up ------------------------------------------------------------------------------------
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, prefetch: torch.Tensor | None = None) -> torch.Tensor:
     """gate_up [T, 2*I] (gate columns first) -> [T, I]."""
     _need_cuda(gate_up)
     _need_contig(gate_up=gate_up)
@@ -147,8 +155,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Te
     if out is None:
         out = torch.empty((T, inter), dtype=gate_up.dtype, device=gate_up.device)
     lib = _lib("elementwise")
-    _check(lib, lib.pi_silu_mul(_p(gate_up), _p(out), c_int(_code(gate_up.dtype)), c_int(T), c_int(inter), _stream()),
-           "silu_mul")
+    _check(lib, lib.pi_silu_mul(_p(gate_up), _p(out), c_int(_code(gate_up.dtype)), c_int(T), c_int(inter),
+                                *_prefetch_args(prefetch), _stream()), "silu_mul")
     return out
 
 
@@ -171,7 +179,8 @@ def rope_table(positions: torch.Tensor, divisors: torch.Tensor):
 # ---- fused per-head norm + rotation + paged key/value write ---------------------------------------------
 def qk_norm_rope_write(qkv: torch.Tensor, q_weight, k_weight, eps: float, cos, sin, adjacent_pairs: bool,
                        kcache, vcache, block_table, token_slot: torch.Tensor, positions: torch.Tensor,
-                       page_size: int, nq: int, nkv: int, head_dim: int, error_count: torch.Tensor) -> None:
+                       page_size: int, nq: int, nkv: int, head_dim: int, error_count: torch.Tensor,
+                       prefetch: torch.Tensor | None = None) -> None:
     """qkv [T, (nq + 2*nkv) * d]: query heads are normalised and rotated in place; key heads are
     normalised, rotated and written to ``kcache``; value heads are copied to ``vcache`` (both
     [pages, nkv, page_size, d]).  ``q_weight``/``k_weight`` None: no per-head norm.  ``cos``/``sin``
@@ -199,8 +208,8 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_weight, k_weight, eps: float, cos, s
         c_int(_code(wdtype)), c_float(eps), c_int(1 if has_norm else 0), _p(cos), _p(sin), c_int(rot_pairs),
         c_int(1 if adjacent_pairs else 0), _p(kcache), _p(vcache), _p(block_table),
         c_int(block_table.shape[1] if block_table is not None else 0), _p(token_slot), _p(positions),
-        c_int(page_size), c_int(nq), c_int(nkv), c_int(head_dim), c_int(T), _p(error_count), _stream()),
-        "qk_norm_rope_write")
+        c_int(page_size), c_int(nq), c_int(nkv), c_int(head_dim), c_int(T), _p(error_count),
+        *_prefetch_args(prefetch), _stream()), "qk_norm_rope_write")
 
 
 # ---- attention ------------------------------------------------------------------------------------------------
@@ -221,6 +230,18 @@ def attention_simple(q: torch.Tensor, q_stride: int, kcache, vcache, block_table
     return out
 
 
+def choose_split_keys(num_decode: int, num_kv_heads: int, max_pos: int) -> int:
+    """Keys per range of the split decode attention.  Short ranges give a small batch enough CTAs to
+    fill the GPU; a large batch has enough already and prefers long ranges (less start-up cost per byte)."""
+    tiles = (max_pos + 256) // 256
+    ctas = num_decode * max(num_kv_heads, 1) * tiles
+    if ctas > 16 * 148:
+        return 1024
+    if ctas > 6 * 148:
+        return 512
+    return SPLIT_KEYS
+
+
 def attention_num_splits(pos: int, window: int | None, split_keys: int = SPLIT_KEYS) -> int:
     """Key ranges a decoding request whose newest token sits at ``pos`` is cut into (depends on its own
     length and the window only, never on the batch)."""
@@ -234,7 +255,7 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
                   token_seg, num_tokens: int, num_segments: int, max_seg_len: int, has_prompt: bool, has_decode: bool,
                   max_splits: int, part_acc, part_ml, nq: int, nkv: int, head_dim: int, page_size: int,
                   window: int | None, scale: float, out: torch.Tensor | None = None,
-                  split_keys: int = SPLIT_KEYS) -> torch.Tensor:
+                  split_keys: int = SPLIT_KEYS, prefetch: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core paged attention for bfloat16 over request segments (see csrc/attention_mma.cu)."""
     _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml)
     _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
@@ -247,12 +268,12 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
         if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:
             raise KernelError("scratch for the split decode attention is missing or too small")
     lib = _lib("attention_mma", head_dim)
-    _check(lib, lib.pi_attention_mma(
+    _check(lib, lib.pi_attention_mma_prefetch(
         _p(q), c_int(q_stride), _p(kcache), _p(vcache), _p(block_table), c_int(block_table.shape[1]), _p(seg_off),
         _p(seg_slot), _p(seg_start), _p(seg_len), _p(token_seg), _p(out), _p(part_acc), _p(part_ml), c_int(max_splits),
         c_int(split_keys), c_int(num_tokens), c_int(num_segments), c_int(max_seg_len), c_int(1 if has_prompt else 0),
         c_int(1 if has_decode else 0), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale),
-        _stream()), "attention_mma",
+        *_prefetch_args(prefetch), _stream()), "attention_mma",
         launches=int(has_prompt) + int(has_decode) + int(has_decode and max_splits > 1))
     return out
 
@@ -277,9 +298,33 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = N
     return out
 
 
+SMALL_M_ROWS = 16         # up to this many rows the weight-streaming kernel is used instead of cuBLAS
+
+
+def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x bf16 [M <= 32, K], weight bf16 [N, K] -> [M, N] in bf16 or fp32: every weight read once."""
+    _need_cuda(x, weight)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise KernelError("gemm_small_m takes bfloat16 operands")
+    if x.stride(-1) != 1 or weight.stride(-1) != 1:
+        raise KernelError("gemm_small_m needs unit stride along k")
+    M, K = x.shape
+    N, K2 = weight.shape
+    if K != K2:
+        raise KernelError(f"inner sizes differ: {K} vs {K2}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    lib = _lib("gemm_small_m")
+    _check(lib, lib.pi_gemm_small_m(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
+                                    c_int(_code(out_dtype)), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
+                                    _stream()), "gemm_small_m")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """y = x W^T with W [out, in] (src/layer/linear.cpp:213).  A bfloat16 weight runs on cuBLAS with
-    32-bit accumulation; a float32 weight runs on the fp32-FMA kernel, whatever the activation dtype."""
+    """y = x W^T with W [out, in] (src/layer/linear.cpp:213).  A bfloat16 weight runs on tensor cores with
+    32-bit accumulation: up to SMALL_M_ROWS rows on the weight-streaming kernel, more on cuBLAS.  A float32
+    weight runs on the fp32-FMA kernel, whatever the activation dtype."""
     _need_cuda(x, weight)
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32:
@@ -288,6 +333,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if weight.dtype != torch.bfloat16:
         raise KernelError(f"weights must be bfloat16 or float32, not {weight.dtype}")
     xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    if (xb.shape[0] <= SMALL_M_ROWS and xb.shape[1] % 8 == 0 and xb.stride(-1) == 1 and xb.stride(0) % 8 == 0
+            and weight.stride(-1) == 1 and weight.stride(0) % 8 == 0 and xb.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32)):
+        return gemm_small_m(xb, weight, out_dtype)
     if out_dtype == torch.bfloat16:
         return torch.mm(xb, weight.t())
     return torch.mm(xb, weight.t(), out_dtype=torch.float32)
@@ -303,7 +352,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     if out is None:
         out = torch.empty((n,), dtype=torch.int32, device=logits.device)
     lib = _lib("sampling")
-    _check(lib, lib.pi_argmax(_p(logits), c_int(logits.stride(0)), c_int(n), c_int(V), _p(out), _stream()), "argmax")
+    words = lib.pi_argmax_scratch_floats(c_int(n), c_int(V))
+    scratch = torch.empty((words,), dtype=torch.float32, device=logits.device) if words else None
+    _check(lib, lib.pi_argmax(_p(logits), c_int(logits.stride(0)), c_int(n), c_int(V), _p(out), _p(scratch), _stream()),
+           "argmax", launches=2 if words else 1)
     return out
 
 

@@ -79,6 +79,9 @@ class Attention(Mixer):
         self._tensors = {"qkv": self.qkv, "o": self.o}
         self.attention_impl = getattr(runtime, "attention_impl", "auto")
 
+    def first_weights(self):
+        return self.qkv
+
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         """x [T, H] in the activation dtype; ``cache`` is the view of this execution's cache
         (key pool, value pool, block table of its group)."""
@@ -89,17 +92,18 @@ class Attention(Mixer):
             qkv, self.q_norm, self.k_norm, self.norm_eps,
             rot["cos"] if rot else None, rot["sin"] if rot else None, rot["adjacent"] if rot else True,
             cache.keys, cache.values, cache.block_table, ctx.token_slot, ctx.positions, cache.page_size,
-            self.num_heads, nkv_written, self.head_dim, ctx.error_count)
+            self.num_heads, nkv_written, self.head_dim, ctx.error_count, prefetch=ctx.prefetch(self.o))
         q_stride = qkv.shape[1]
         use_mma = (ctx.act_dtype == torch.bfloat16 and self.attention_impl != "simple"
                    and self.head_dim % 16 == 0 and self.head_dim <= 256)
         if use_mma:
-            scratch = ctx.attention_scratch(self.num_heads, self.head_dim, self.window)
+            scratch = ctx.attention_scratch(self.num_heads, self.head_dim, self.window, self.num_kv_heads)
             attn = ops.attention_mma(
                 qkv, q_stride, cache.keys, cache.values, cache.block_table, ctx.seg_off, ctx.seg_slot, ctx.seg_start,
                 ctx.seg_len, ctx.token_seg, ctx.num_tokens, ctx.num_segments, ctx.max_seg_len, ctx.has_prompt,
                 ctx.has_decode, scratch.max_splits, scratch.acc, scratch.ml, self.num_heads, self.num_kv_heads,
-                self.head_dim, cache.page_size, self.window, self.scale)
+                self.head_dim, cache.page_size, self.window, self.scale, split_keys=scratch.split_keys,
+                prefetch=ctx.prefetch(getattr(ctx, "upcoming_weights", None)))
         else:
             attn = ops.attention_simple(
                 qkv, q_stride, cache.keys, cache.values, cache.block_table, ctx.token_slot, ctx.positions,

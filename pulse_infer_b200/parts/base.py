@@ -58,6 +58,11 @@ class Part:
     def num_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in getattr(self, "_tensors", {}).values())
 
+    def first_weights(self):
+        """The weight tensor this part's forward streams first, if any: the kernel that runs just before
+        it may ask the L2 to start fetching it (see ``StepContext.prefetch``)."""
+        return None
+
 
 class Mixer(Part):
     def cache_spec(self) -> CacheSpec | None:
@@ -79,8 +84,10 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
 
-    def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None):
-        """residual (fp32, updated in place unless ``rows`` is given) += delta; returns norm(residual)."""
+    def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None,
+                 upcoming=None):
+        """residual (fp32, updated in place unless ``rows`` is given) += delta; returns norm(residual).
+        ``upcoming``: weights the next product will stream (a prefetch hint, may be ignored)."""
         raise NotImplementedError
 
 

@@ -18,7 +18,9 @@ class PreNormBlock(Block):
         self.feed_forward_norm = feed_forward_norm
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
-        x = self.mixer_norm.add_norm(stream.hidden, stream.pending, ctx)
+        x = self.mixer_norm.add_norm(stream.hidden, stream.pending, ctx, upcoming=self.mixer.first_weights())
+        ctx.upcoming_weights = self.feed_forward.first_weights()      # for the mixer's last small kernel
         stream.pending = self.mixer.forward(x, ctx, cache)
-        x = self.feed_forward_norm.add_norm(stream.hidden, stream.pending, ctx)
+        ctx.upcoming_weights = None
+        x = self.feed_forward_norm.add_norm(stream.hidden, stream.pending, ctx, upcoming=self.feed_forward.first_weights())
         stream.pending = self.feed_forward.forward(x, ctx)

@@ -34,7 +34,10 @@ class SwiGLU(FeedForward):
         self.down = tensors["down_proj.weight"].contiguous()
         self._tensors = {"gate_up": self.gate_up, "down": self.down}
 
+    def first_weights(self):
+        return self.gate_up
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         gu = ops.linear(x, self.gate_up, ctx.act_dtype)
-        act = ops.silu_mul(gu)
+        act = ops.silu_mul(gu, prefetch=ctx.prefetch(self.down))
         return ops.linear(act, self.down, ctx.act_dtype)

@@ -46,6 +46,9 @@ class LMHead(Part):
         self.weight = tensors.get("weight")
         self._tensors = {} if self.weight is None else {"weight": self.weight}
 
+    def first_weights(self):
+        return self.weight
+
     def tie_to(self, table: torch.Tensor) -> None:
         self.weight = table
 

@@ -140,5 +140,6 @@ class DecoderModel:
             block.forward(stream, ctx, cache)
         if ctx.num_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=hidden.device)
-        x = self.final_norm.add_norm(stream.hidden, stream.pending, ctx, rows=ctx.want_rows)
+        x = self.final_norm.add_norm(stream.hidden, stream.pending, ctx, rows=ctx.want_rows,
+                                     upcoming=self.lm_head.first_weights())
         return self.lm_head.forward(x, ctx)

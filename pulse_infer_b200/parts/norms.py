@@ -29,5 +29,6 @@ class RMSNorm(Norm):
         """x is a 32-bit residual [n, size]; returns the norm in the activation dtype."""
         return ops.add_rmsnorm(x, None, self.weight, self.eps, ctx.act_dtype)
 
-    def add_norm(self, residual: torch.Tensor, delta, ctx, rows=None) -> torch.Tensor:
-        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.act_dtype, rows=rows)
+    def add_norm(self, residual: torch.Tensor, delta, ctx, rows=None, upcoming=None) -> torch.Tensor:
+        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.act_dtype, rows=rows,
+                               prefetch=ctx.prefetch(upcoming))

@@ -26,7 +26,7 @@ def test_embedding(dtype):
     assert out.dtype == torch.float32 and torch.equal(out, want)
 
 
-@pytest.mark.parametrize("hidden", [4096, 202, 77])
+@pytest.mark.parametrize("hidden", [4096, 202, 77, 1536, 5120, 8192, 9000])
 @pytest.mark.parametrize("act,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                      (torch.bfloat16, torch.float32)])
 def test_add_rmsnorm(hidden, act, wdt):
@@ -242,6 +242,25 @@ def test_gemm_f32_true_32bit(M, N, K):
     # a row's result does not depend on the rows around it
     one = ops.gemm_f32(x[M // 2:M // 2 + 1].contiguous().to(dev), w.to(dev)).cpu()
     assert torch.equal(one[0], out[M // 2])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("N,K", [(515, 96), (4096, 4096), (64, 8), (1000, 12288), (50, 200)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_small_m(M, N, K, out_dtype):
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    out = ops.gemm_small_m(x.to(dev), w.to(dev), out_dtype).cpu()
+    want = x.double() @ w.double().t()
+    err = float((out.double() - want).abs().max())
+    scale = float(want.abs().max())
+    assert err <= (2e-5 if out_dtype == torch.float32 else 2 ** -8) * scale + 1e-6
+    # a row's result does not depend on the rows around it
+    if M > 1:
+        one = ops.gemm_small_m(x[M - 1:].contiguous().to(dev), w.to(dev), out_dtype).cpu()
+        assert torch.equal(one[0], out[M - 1])
 
 
 def test_linear_bfloat16_and_mixed():
