@@ -403,6 +403,286 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Decoding, second form: one new token per request, so a (request, kv head) has only G = nq / nkv query
+// rows.  Here the operands are swapped: the 16-row side of the mma holds 16 KEYS and the 8-column side
+// holds the query rows (no padding of 4 rows to 16, half the accumulator registers, half the mma count):
+//     S^T[key, row] = K[key, :] . Q[row, :]         A = K slice (16 keys x d),   B = Q^T
+//     O^T[dim, row] += V^T[dim, key] P^T[key, row]  A = V^T (ldmatrix.trans),    B = P^T (movmatrix of S^T)
+// K goes from global memory straight into A fragments (16-byte loads; the d index is permuted inside
+// 32-wide blocks, identically for K and Q, which a dot product does not notice); only V is staged in shared
+// memory, per warp, by cp.async three slices deep.  The four warps of a CTA take the 16-key slices of the
+// CTA's key range in turn and never wait for one another until the final merge, so 16 warps per SM keep
+// loads in flight.  Needs D % 32 == 0 and G <= 8 * NT.
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+    unsigned d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint4 ldg_stream16(const void* ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
+
+// CONTIG: the page size is a multiple of 16, so the 16 keys of a slice are 16 consecutive rows of one page and a
+// slice needs one table lookup and no exchange of offsets between lanes.
+template <int D, int NT, bool CONTIG>
+__global__ void __launch_bounds__(128, (D * NT <= 128) ? 4 : 2) attn_decode_kernel(const AttnParams p) {
+    constexpr int LDS = D + 8;
+    constexpr int CHUNKS = D / 8;
+    constexpr int DB = D / 32;             // 32-wide blocks of d
+    constexpr int VSTAGES = 3;
+    constexpr int WARPS = 4;
+    static_assert(D % 32 == 0, "this kernel takes head sizes that are multiples of 32");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_wait();
+    pdl_trigger(PDL_ATTENTION);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int seg = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    if (p.seg_len[seg] != 1) return;
+    const int G = p.group;
+    const int pos = p.seg_start[seg];
+    const int tok = p.seg_off[seg];
+    const int* table = p.block_table + (size_t)p.seg_slot[seg] * p.bt_stride;
+    const int lo = window_lo(pos, p.window);
+    const int nsplits = decode_num_splits(pos, p.window, p.split_keys);
+    if (split >= nsplits) return;
+    const int kbegin = (lo / BN) * BN + split * p.split_keys;
+    const int kend = min(pos + 1, kbegin + p.split_keys);
+    const int nslices = (kend - kbegin + 15) / 16;
+
+    bf16* vs = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * VSTAGES * 16 * LDS;   // this warp's V stages
+
+    // ---- Q as B fragments: row 8*nt + g, elements 32*db + 8*t .. +7 -------------------------------------
+    uint4 qf[NT][DB];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int r = 8 * nt + g;
+        const bf16* qrow = p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + (r < G ? r : 0)) * D + 8 * t;
+#pragma unroll
+        for (int db = 0; db < DB; ++db)
+            qf[nt][db] = r < G ? *reinterpret_cast<const uint4*>(qrow + 32 * db) : make_uint4(0, 0, 0, 0);
+    }
+
+    // ---- per-slice helpers ---------------------------------------------------------------------------------
+    // What a lane keeps about a slice: CONTIG - the element offset of the slice's first key (same in every lane);
+    // otherwise - the offset of key (lane & 15), exchanged by shuffles when rows are addressed.  ~0: no such key.
+    auto slice_offsets = [&](int slice) -> size_t {
+        const int j = kbegin + 16 * slice + (CONTIG ? 0 : (lane & 15));
+        size_t off = ~(size_t)0;
+        if (slice < nslices && j < kend) {
+            const int page = table[j / p.page_size];
+            if (page >= 0) off = (((size_t)page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * D;
+        }
+        return off;
+    };
+    auto offset_of_row = [&](size_t mine, int row) -> size_t {
+        if (CONTIG) return mine == ~(size_t)0 ? mine : mine + (size_t)row * D;
+        const unsigned lo32 = __shfl_sync(0xffffffffu, (unsigned)(mine & 0xffffffffu), row);
+        const unsigned hi32 = __shfl_sync(0xffffffffu, (unsigned)(mine >> 32), row);
+        return ((size_t)hi32 << 32) | lo32;
+    };
+    auto load_v = [&](size_t mine, int slice, int stage) {      // 16 rows x CHUNKS 16-byte pieces, 32 lanes
+        bf16* dst = vs + stage * 16 * LDS;
+        const int rows_valid = kend - (kbegin + 16 * slice);     // rows beyond the range are zero-filled
+#pragma unroll
+        for (int c = 0; c < (16 * CHUNKS) / 32; ++c) {
+            const int idx = lane + 32 * c;
+            const int r = idx / CHUNKS, ch = idx % CHUNKS;
+            const size_t off = offset_of_row(mine, r);
+            const bool valid = off != ~(size_t)0 && r < rows_valid;
+            cp_async16(dst + r * LDS + ch * 8, p.vcache + (valid ? off + ch * 8 : 0), valid);
+        }
+    };
+    auto load_k = [&](size_t mine, uint4 (&ka)[DB], uint4 (&kb)[DB]) {   // keys g and g + 8 of the slice
+        // rows beyond the range but inside the page hold old finite data; their scores are masked below
+        const size_t oa = offset_of_row(mine, g), ob = offset_of_row(mine, g + 8);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+            ka[db] = oa != ~(size_t)0 ? ldg_stream16(p.kcache + oa + 32 * db + 8 * t) : make_uint4(0, 0, 0, 0);
+            kb[db] = ob != ~(size_t)0 ? ldg_stream16(p.kcache + ob + 32 * db + 8 * t) : make_uint4(0, 0, 0, 0);
+        }
+    };
+
+    float m_r[NT][2], l_r[NT][2];
+    float o[D / 16][NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { m_r[nt][0] = -INFINITY; m_r[nt][1] = -INFINITY; l_r[nt][0] = 0.0f; l_r[nt][1] = 0.0f; }
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { o[dt][nt][0] = 0.0f; o[dt][nt][1] = 0.0f; o[dt][nt][2] = 0.0f; o[dt][nt][3] = 0.0f; }
+
+    // ---- this warp's slices: warp, warp + 4, ... ---------------------------------------------------------------
+    const int n_mine = nslices > warp ? (nslices - warp + WARPS - 1) / WARPS : 0;
+    size_t off0 = slice_offsets(warp), off1 = slice_offsets(warp + WARPS);
+    if (n_mine > 0) load_v(off0, warp, 0);
+    cp_async_commit();
+    if (n_mine > 1) load_v(off1, warp + WARPS, 1);
+    cp_async_commit();
+    uint4 ka[DB], kb[DB];
+    if (n_mine > 0) load_k(off0, ka, kb);
+
+    for (int i = 0; i < n_mine; ++i) {
+        __syncwarp();                                        // everyone has finished reading the stage refilled below
+        const size_t off2 = slice_offsets(warp + WARPS * (i + 2));
+        if (i + 2 < n_mine) load_v(off2, warp + WARPS * (i + 2), (i + 2) % VSTAGES);
+        cp_async_commit();
+
+        // S^T = K Q^T : 16 keys x 8 rows per tile of rows
+        const int k0 = kbegin + 16 * (warp + WARPS * i);
+        float s[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { s[nt][0] = 0.0f; s[nt][1] = 0.0f; s[nt][2] = 0.0f; s[nt][3] = 0.0f; }
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const unsigned a1[4] = {ka[db].x, kb[db].x, ka[db].y, kb[db].y};
+                const unsigned a2[4] = {ka[db].z, kb[db].z, ka[db].w, kb[db].w};
+                mma_bf16(s[nt], a1, qf[nt][db].x, qf[nt][db].y);
+                mma_bf16(s[nt], a2, qf[nt][db].z, qf[nt][db].w);
+            }
+        }
+        if (i + 1 < n_mine) load_k(off1, ka, kb);            // next slice's keys: in flight during softmax and P V
+        // visibility depends on the key only (one query position): keys k0 + g and k0 + g + 8
+        const int ja = k0 + g, jb = ja + 8;
+        const bool va = ja <= pos && ja >= lo && ja < kend, vb = jb <= pos && jb >= lo && jb < kend;
+        unsigned pb0[NT], pb1[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float alpha[2];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {                    // c: row 2t + c of this tile
+                const float sa = va ? s[nt][c] * p.scale_log2 : -INFINITY;
+                const float sb = vb ? s[nt][2 + c] * p.scale_log2 : -INFINITY;
+                float mx = fmaxf(sa, sb);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_new = fmaxf(m_r[nt][c], mx);
+                const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+                alpha[c] = exp2f(m_r[nt][c] - base);
+                m_r[nt][c] = m_new;
+                const float pa = exp2f(sa - base), pbv = exp2f(sb - base);
+                s[nt][c] = pa;
+                s[nt][2 + c] = pbv;
+                l_r[nt][c] = l_r[nt][c] * alpha[c] + pa + pbv;   // this lane's keys only; summed over g at the end
+            }
+            if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {   // the maximum moved for some row
+#pragma unroll
+                for (int dt = 0; dt < D / 16; ++dt) {
+                    o[dt][nt][0] *= alpha[0]; o[dt][nt][1] *= alpha[1];
+                    o[dt][nt][2] *= alpha[0]; o[dt][nt][3] *= alpha[1];
+                }
+            }
+            // P^T as B operand: transpose the two 8x8 blocks (keys 0-7 | 8-15) x (rows 0-7)
+            pb0[nt] = movmatrix_trans(pack_bf16(s[nt][0], s[nt][1]));
+            pb1[nt] = movmatrix_trans(pack_bf16(s[nt][2], s[nt][3]));
+        }
+
+        cp_async_wait<2>();                                  // V of slice i has landed (two younger groups may fly)
+        __syncwarp();
+        const bf16* vt = vs + (i % VSTAGES) * 16 * LDS;
+#pragma unroll
+        for (int dt = 0; dt < D / 16; ++dt) {
+            unsigned a[4];
+            ldmatrix_x4_trans(a, vt + ((lane & 7) + 8 * (lane >> 4)) * LDS + dt * 16 + 8 * ((lane >> 3) & 1));
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma_bf16(o[dt][nt], a, pb0[nt], pb1[nt]);
+        }
+        off1 = off2;
+    }
+    cp_async_wait<0>();
+
+    // ---- merge the four warps -----------------------------------------------------------------------------------
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            float v = l_r[nt][c];
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            l_r[nt][c] = v;
+        }
+    __syncthreads();                                         // all warps are done with their V stages
+    constexpr int ROWS = 8 * NT;
+    float* mo = reinterpret_cast<float*>(smem_raw);          // [WARPS][ROWS][D]
+    float* mm = mo + WARPS * ROWS * D;                       // [WARPS][ROWS]
+    float* ml = mm + WARPS * ROWS;                           // [WARPS][ROWS]
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int r = 8 * nt + 2 * t + c;
+            float* dst = mo + (warp * ROWS + r) * D;
+#pragma unroll
+            for (int dt = 0; dt < D / 16; ++dt) {
+                dst[dt * 16 + g] = o[dt][nt][c];
+                dst[dt * 16 + g + 8] = o[dt][nt][2 + c];
+            }
+            if (g == 0) { mm[warp * ROWS + r] = m_r[nt][c]; ml[warp * ROWS + r] = l_r[nt][c]; }
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += 128) {
+        const int r = idx / D, e = idx % D;
+        float mstar = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mstar = fmaxf(mstar, mm[w * ROWS + r]);
+        float lsum = 0.0f, acc = 0.0f;
+        if (mstar != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float f = exp2f(mm[w * ROWS + r] - mstar);
+                lsum += ml[w * ROWS + r] * f;
+                acc += mo[(w * ROWS + r) * D + e] * f;
+            }
+        }
+        const size_t orow = (size_t)tok * p.nq + (size_t)(kvh * G + r);
+        if (nsplits == 1) {
+            p.out[orow * D + e] = __float2bfloat16_rn(lsum > 0.0f ? acc / lsum : 0.0f);
+        } else {
+            p.part_acc[(orow * p.max_splits + split) * D + e] = acc;
+            if (e == 0) {
+                p.part_ml[(orow * p.max_splits + split) * 2] = mstar;
+                p.part_ml[(orow * p.max_splits + split) * 2 + 1] = lsum;
+            }
+        }
+    }
+}
+
+template <int NT>
+static size_t attn_decode_smem_bytes() {
+    const size_t stages = (size_t)4 * 3 * 16 * (PI_HEAD_DIM + 8) * sizeof(bf16);
+    const size_t merge = (size_t)4 * 8 * NT * (PI_HEAD_DIM + 2) * sizeof(float);
+    return stages > merge ? stages : merge;
+}
+
+#if PI_HEAD_DIM % 32 == 0
+template <int NT, bool CONTIG>
+static int launch_attn_decode(const AttnParams& p, int num_segments, int splits, cudaStream_t stream) {
+    static bool configured = false;
+    const size_t smem = attn_decode_smem_bytes<NT>();
+    auto kernel = attn_decode_kernel<PI_HEAD_DIM, NT, CONTIG>;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) {
+            snprintf(g_pi_error, sizeof(g_pi_error), "attention: cannot reserve %zu bytes of shared memory: %s", smem,
+                     cudaGetErrorString(err));
+            return (int)err;
+        }
+        configured = true;
+    }
+    pi_launch(kernel, dim3((unsigned)num_segments, p.nkv, splits), dim3(128), smem, stream, p);
+    return pi_check_launch("pi_attention_mma decode");
+}
+#endif
+
 // Combine the key ranges of decode-mode rows: one block per (token, head).
 template <int D>
 __global__ void attn_merge_kernel(const AttnParams p, const int* __restrict__ token_seg, const Prefetch pf) {
@@ -510,7 +790,16 @@ PI_EXPORT int pi_attention_mma_prefetch(const void* q, int q_stride, const void*
         if (max_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return pi_refuse("pi_attention_mma: scratch for %d key ranges is missing", max_splits);
         p.decode = 1;
         p.tiles_per_seg = (p.group + 15) / 16;
+#if PI_HEAD_DIM % 32 == 0
+        const bool contig = page_size % 16 == 0;
+        if (p.group <= 8) rc = contig ? launch_attn_decode<1, true>(p, num_segments, max_splits, stream)
+                                      : launch_attn_decode<1, false>(p, num_segments, max_splits, stream);
+        else if (p.group <= 16) rc = contig ? launch_attn_decode<2, true>(p, num_segments, max_splits, stream)
+                                            : launch_attn_decode<2, false>(p, num_segments, max_splits, stream);
+        else rc = launch_attn<1, 4, 3>(p, num_segments, max_splits, stream);
+#else
         rc = launch_attn<1, 4, 3>(p, num_segments, max_splits, stream);
+#endif
         if (rc) return rc;
         if (max_splits > 1) {
             const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, num_tokens * nq);

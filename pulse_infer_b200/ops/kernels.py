@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -233,8 +234,13 @@ def attention_simple(q: torch.Tensor, q_stride: int, kcache, vcache, block_table
 def choose_split_keys(num_decode: int, num_kv_heads: int, max_pos: int) -> int:
     """Keys per range of the split decode attention.  Short ranges give a small batch enough CTAs to
     fill the GPU; a large batch has enough already and prefers long ranges (less start-up cost per byte)."""
+    forced = os.environ.get("PULSE_SPLIT_KEYS")
+    if forced:
+        return int(forced)
     tiles = (max_pos + 256) // 256
     ctas = num_decode * max(num_kv_heads, 1) * tiles
+    if ctas > 48 * 148:
+        return 2048
     if ctas > 16 * 148:
         return 1024
     if ctas > 6 * 148:

@@ -174,7 +174,7 @@ def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengt
 
 ATTN_SHAPES = [  # nq, nkv, d, page
     (4, 2, 16, 8), (8, 1, 32, 16), (6, 2, 48, 16), (3, 3, 64, 4), (32, 8, 128, 16), (5, 1, 80, 8), (2, 1, 256, 16),
-    (40, 2, 64, 16)]
+    (40, 2, 64, 16), (12, 1, 64, 16), (16, 1, 32, 8), (7, 7, 96, 16)]
 
 
 @pytest.mark.parametrize("nq,nkv,d,page", ATTN_SHAPES)
