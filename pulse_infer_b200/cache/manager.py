@@ -147,13 +147,24 @@ class CacheManager:
     def free_pages(self) -> list[int]:
         return [g.allocator.num_free for g in self.groups]
 
+    def _covered(self, slot: int, new_length: int) -> bool:
+        """True when the pages already reserved for the slot reach new_length (the common decode case)."""
+        page = self.page_size
+        return new_length <= (int(self._reserved[slot]) + page - 1) // page * page
+
     def can_reserve(self, request_id, new_length: int) -> bool:
+        if self._covered(self.slot(request_id), new_length):
+            return new_length <= self.max_pages_per_request * self.page_size
         return all(n <= g.allocator.num_free for n, g in zip(self.pages_needed(request_id, new_length), self.groups))
 
     def reserve(self, request_id, new_length: int) -> None:
         """Make sure every group holds pages for positions < new_length.  Atomic: on OutOfPages
         nothing has changed."""
         slot = self.slot(request_id)
+        if self._covered(slot, new_length) and new_length <= self.max_pages_per_request * self.page_size:
+            if new_length > self._reserved[slot]:
+                self._reserved[slot] = new_length
+            return
         if new_length > self.max_pages_per_request * self.page_size:
             raise CacheError(f"request '{request_id}' would reach {new_length} tokens, beyond the "
                              f"{self.max_pages_per_request * self.page_size} this cache was sized for")

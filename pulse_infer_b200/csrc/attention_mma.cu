@@ -50,6 +50,7 @@ struct AttnParams {
     int window;            // 0: all keys
     float scale_log2;      // log2(e) / sqrt(D)
     int tiles_per_seg;
+    int num_segments;
     int split_keys;        // keys per range in decode mode (a multiple of BN)
     int decode;            // 1: handle segments of one token only; 0: handle the others only
 };
@@ -110,8 +111,21 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
     pdl_trigger(PDL_ATTENTION);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wr = warp / KEY_WARPS, wk = warp % KEY_WARPS;
-    const int seg = blockIdx.x / p.tiles_per_seg, tile = blockIdx.x % p.tiles_per_seg;
-    const int kvh = blockIdx.y, split = blockIdx.z;
+    // Prompt mode: a linear grid ordered so that, for every kv head in turn, the tiles with the most keys (the
+    // last rows of a portion) start first; the light tiles fill the tail.  Decode mode: (row tile, kv head, range).
+    int seg, tile, kvh, split;
+    if (KEY_WARPS == 1) {
+        kvh = blockIdx.x % p.nkv;
+        const int rest = blockIdx.x / p.nkv;
+        tile = p.tiles_per_seg - 1 - rest / p.num_segments;
+        seg = rest % p.num_segments;
+        split = 0;
+    } else {
+        seg = blockIdx.x / p.tiles_per_seg;
+        tile = blockIdx.x % p.tiles_per_seg;
+        kvh = blockIdx.y;
+        split = blockIdx.z;
+    }
 
     const int len = p.seg_len[seg];
     if ((len == 1) != (p.decode != 0)) return;
@@ -731,7 +745,9 @@ static int launch_attn(const AttnParams& p, int num_segments, int splits, cudaSt
         }
         configured = true;
     }
-    dim3 grid((unsigned)num_segments * p.tiles_per_seg, p.nkv, splits);
+    const long long linear = (long long)num_segments * p.tiles_per_seg * p.nkv;
+    if (KEY_WARPS == 1 && linear > 2147483647LL) return pi_refuse("pi_attention_mma: %lld tiles are beyond the grid limit", linear);
+    const dim3 grid = KEY_WARPS == 1 ? dim3((unsigned)linear, 1, 1) : dim3((unsigned)num_segments * p.tiles_per_seg, p.nkv, splits);
     pi_launch(kernel, grid, dim3(ROW_WARPS * KEY_WARPS * 32), smem, stream, p);
     return pi_check_launch("pi_attention_mma");
 }
@@ -772,6 +788,7 @@ PI_EXPORT int pi_attention_mma_prefetch(const void* q, int q_stride, const void*
     p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.page_size = page_size; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.split_keys = split_keys;
+    p.num_segments = num_segments;
     int rc = 0;
     if (has_prompt) {
         p.decode = 0;

@@ -70,9 +70,11 @@ class ContinuousBatchEngine:
             req.add_computed_tokens(n)
         sampled = []
         if sampling_reqs:
+            history = None
+            if any(r.sampling.presence_penalty > 0.0 for r in sampling_reqs):
+                history = [r.all_tokens() if r.sampling.presence_penalty > 0.0 else () for r in sampling_reqs]
             tokens = self.sampler.sample(logits, [r.sampling for r in sampling_reqs],
-                                         [r.num_generated() for r in sampling_reqs],
-                                         [r.all_tokens() for r in sampling_reqs])
+                                         [r.num_generated() for r in sampling_reqs], history)
             for req, tok in zip(sampling_reqs, tokens):
                 keep_going = req.add_sampled_token(int(tok), self.eos_token_ids)
                 sampled.append((req.request_id, int(tok)))

@@ -55,7 +55,10 @@ class InferenceRequest:
         """Feeding tokens that are already known: the prompt (inference_request.hpp:73-75), or, after a
         preemption, prompt plus the tokens generated so far.  A decoding request has exactly one
         pending token, the one it sampled last."""
-        return not self.is_finished() and (self.num_generated() == 0 or self.pending_tokens() > 1)
+        if self.state == RequestState.FINISHED:
+            return False
+        generated = len(self.generated_tokens)
+        return generated == 0 or len(self.prompt_tokens) + generated - self.num_computed_tokens > 1
 
     def has_pending_input(self) -> bool:
         return not self.is_finished() and self.num_computed_tokens < self.total_input_tokens()
@@ -92,7 +95,12 @@ class InferenceRequest:
 
     def get_next_chunk_tokens(self, chunk_size: int = 256) -> list:
         n = self.get_next_chunk_size(chunk_size)
-        return self.all_tokens()[self.num_computed_tokens:self.num_computed_tokens + n]
+        at, split = self.num_computed_tokens, len(self.prompt_tokens)
+        if at >= split:                      # decoding: only generated tokens are touched
+            return self.generated_tokens[at - split:at - split + n]
+        if at + n <= split:
+            return self.prompt_tokens[at:at + n]
+        return self.prompt_tokens[at:] + self.generated_tokens[:at + n - split]
 
     def add_computed_tokens(self, count: int) -> None:
         if count <= 0:

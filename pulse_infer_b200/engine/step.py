@@ -60,10 +60,11 @@ class ModelRunner:
             if n == 0:
                 raise StepError(f"request '{s.request_id}' brings no tokens")
             total += n
-            for t in s.tokens:
-                if not (0 <= t < self.vocab_size):
-                    raise StepError(f"request '{s.request_id}': token id {t} is outside the vocabulary "
-                                    f"[0, {self.vocab_size})")
+            lowest, highest = (s.tokens[0], s.tokens[0]) if n == 1 else (min(s.tokens), max(s.tokens))
+            if lowest < 0 or highest >= self.vocab_size:
+                bad = lowest if lowest < 0 else highest
+                raise StepError(f"request '{s.request_id}': token id {bad} is outside the vocabulary "
+                                f"[0, {self.vocab_size})")
             s.slot = self.cache.slot(s.request_id)
             s.start = self.cache.length(s.request_id)
             if s.start + n > self.max_position:
