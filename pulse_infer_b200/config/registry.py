@@ -56,6 +56,8 @@ def architecture_name_of(obj: dict, source: str) -> str:
     model_type = obj.get("model_type")
     if isinstance(model_type, str) and model_type in _MODEL_TYPES:
         return _MODEL_TYPES[model_type]
+    if not archs and not model_type and len(_ARCHITECTURES) == 1:
+        return next(iter(_ARCHITECTURES))      # the file names nothing and there is only one to choose from
     raise ConfigError(f"'{source}' names no architecture (key 'architectures'); known: "
                       f"{', '.join(sorted(_ARCHITECTURES))}")
 

@@ -6,6 +6,9 @@
 //
 // A CTA owns 16 output features; its warps split K into contiguous ranges and their partial sums are added
 // in warp order through shared memory, so a result does not depend on the launch or on the other rows.
+// Wide outputs (thousands of 16-feature tiles) use 8 warps per CTA with two register sets of weights in
+// flight; narrow ones (N = 4096 gives only 256 tiles) use 16 warps per CTA so that the whole GPU still has
+// loads in flight.
 // (Splitting K further across the CTAs of a thread-block cluster, reduced through distributed shared memory,
 // was measured and dropped: it made the 33-100 MB products of a decode step slower, not faster.)
 //
@@ -18,7 +21,6 @@
 // (src/layer/linear.cpp:213).
 #include "common.cuh"
 
-#define SM_WARPS 8          // warps per CTA, each takes 1/8 of K
 #define SM_FEATURES 16      // output features per CTA
 #define SM_UNROLL 4         // k blocks in flight per warp
 
@@ -36,10 +38,11 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], unsigned a0, unsigned a
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, typename TO>   // MT: tiles of 8 rows of x
-__global__ void __launch_bounds__(SM_WARPS * 32) gemm_small_m_kernel(const bf16* __restrict__ x, int ldx,
-                                                                     const bf16* __restrict__ W, int ldw,
-                                                                     TO* __restrict__ out, int ldo, int M, int N, int K) {
+// MT: tiles of 8 rows of x; SM_WARPS: warps per CTA, each takes 1/SM_WARPS of K; DOUBLE: two register sets
+template <int MT, typename TO, int SM_WARPS, bool DOUBLE, int MIN_CTAS>
+__global__ void __launch_bounds__(SM_WARPS * 32, MIN_CTAS)
+gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw, TO* __restrict__ out, int ldo,
+                    int M, int N, int K) {
     __shared__ float partial[SM_WARPS][SM_FEATURES][MT * 8 + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -64,7 +67,7 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_small_m_kernel(const bf16*
 
     // Two register sets of SM_UNROLL blocks each: while one is multiplied the other is in flight.  The first
     // set is requested before pdl_wait(): weights do not depend on the kernel that produces x.
-    uint4 va0[SM_UNROLL], vb0[SM_UNROLL], va1[SM_UNROLL], vb1[SM_UNROLL];
+    uint4 va0[SM_UNROLL], vb0[SM_UNROLL];
     auto load_w = [&](int b, uint4 (&va)[SM_UNROLL], uint4 (&vb)[SM_UNROLL]) {
 #pragma unroll
         for (int u = 0; u < SM_UNROLL; ++u) {
@@ -91,11 +94,19 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_small_m_kernel(const bf16*
     load_w(b_begin, va0, vb0);
     pdl_wait();
     pdl_trigger(PDL_PRODUCT);
-    for (int b = b_begin; b < b_end; b += 2 * SM_UNROLL) {
-        load_w(b + SM_UNROLL, va1, vb1);
-        multiply(b, va0, vb0);
-        load_w(b + 2 * SM_UNROLL, va0, vb0);
-        multiply(b + SM_UNROLL, va1, vb1);
+    if (DOUBLE) {
+        uint4 va1[SM_UNROLL], vb1[SM_UNROLL];
+        for (int b = b_begin; b < b_end; b += 2 * SM_UNROLL) {
+            load_w(b + SM_UNROLL, va1, vb1);
+            multiply(b, va0, vb0);
+            load_w(b + 2 * SM_UNROLL, va0, vb0);
+            multiply(b + SM_UNROLL, va1, vb1);
+        }
+    } else {
+        for (int b = b_begin; b < b_end; b += SM_UNROLL) {
+            multiply(b, va0, vb0);
+            load_w(b + SM_UNROLL, va0, vb0);
+        }
     }
 
     // acc[i][0..1]: feature g, rows 8i + 2t, 8i + 2t + 1;  acc[i][2..3]: feature g + 8, same rows
@@ -117,20 +128,44 @@ __global__ void __launch_bounds__(SM_WARPS * 32) gemm_small_m_kernel(const bf16*
     }
 }
 
-template <int MT>
-static void launch_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                           int K, cudaStream_t stream) {
+template <int MT, int WARPS, bool DOUBLE, int MIN_CTAS>
+static void launch_small_m_shape(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M,
+                                 int N, int K, cudaStream_t stream) {
     const dim3 grid((unsigned)((N + SM_FEATURES - 1) / SM_FEATURES));
     if (out_dtype == PI_F32)
-        pi_launch(gemm_small_m_kernel<MT, float>, grid, dim3(SM_WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (float*)out, ldo, M, N, K);
+        pi_launch(gemm_small_m_kernel<MT, float, WARPS, DOUBLE, MIN_CTAS>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (float*)out, ldo, M, N, K);
     else
-        pi_launch(gemm_small_m_kernel<MT, bf16>, grid, dim3(SM_WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K);
+        pi_launch(gemm_small_m_kernel<MT, bf16, WARPS, DOUBLE, MIN_CTAS>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K);
+}
+
+// variant 0: chosen from the shape.  1: 8 warps, two register sets, 2 CTAs/SM.  2: 8 warps, two sets, 3 CTAs/SM.
+// 3: 16 warps, one set, 2 CTAs/SM (M <= 8 only).  4: 8 warps, one set, 4 CTAs/SM.
+template <int MT>
+static void launch_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                           int K, int variant, cudaStream_t stream) {
+    const int tiles = (N + SM_FEATURES - 1) / SM_FEATURES;
+    if (variant == 0) {   // from measurements on B200 at the sizes of 8B- to 32B-class models
+        if (MT == 1) {
+            if (tiles <= 2 * 148) variant = K >= 8192 ? 3 : 1;   // few tiles: deep K wants more warps per tile
+            else if (tiles <= 1000) variant = 2;
+            else variant = 4;                                    // many waves: light CTAs, four per SM
+        } else {
+            variant = tiles <= 2 * 148 ? 1 : 2;
+        }
+    }
+    if (variant == 3 && MT != 1) variant = 1;
+    switch (variant) {
+        case 2: launch_small_m_shape<MT, 8, true, 3>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
+        case 3: launch_small_m_shape<1, 16, false, 2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
+        case 4: launch_small_m_shape<MT, 8, false, 4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
+        default: launch_small_m_shape<MT, 8, true, 2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
+    }
 }
 
 PI_EXPORT int pi_gemm_small_m_max_rows() { return 32; }
 
-PI_EXPORT int pi_gemm_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                              int K, cudaStream_t stream) {
+static int gemm_small_m_impl(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                             int K, int variant, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 32) return pi_refuse("pi_gemm_small_m: %d rows; this kernel takes at most 32", M);
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
@@ -138,8 +173,19 @@ PI_EXPORT int pi_gemm_small_m(const void* x, int ldx, const void* W, int ldw, vo
     if (ldx < K || ldw < K || ldo < N) return pi_refuse("pi_gemm_small_m: leading dimensions (%d, %d, %d) too small", ldx, ldw, ldo);
     if (((uintptr_t)x | (uintptr_t)W) & 15) return pi_refuse("pi_gemm_small_m: operands must be 16-byte aligned");
     if (out_dtype != PI_F32 && out_dtype != PI_BF16) return pi_refuse("pi_gemm_small_m: unknown output dtype code %d", out_dtype);
-    if (M <= 8) launch_small_m<1>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream);
-    else if (M <= 16) launch_small_m<2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream);
-    else launch_small_m<4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream);
+    if (M <= 8) launch_small_m<1>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
+    else if (M <= 16) launch_small_m<2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
+    else launch_small_m<4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
     return pi_check_launch("pi_gemm_small_m");
+}
+
+PI_EXPORT int pi_gemm_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
+                              int K, cudaStream_t stream) {
+    return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, 0, stream);
+}
+
+// the same with the launch shape forced (for measurements)
+PI_EXPORT int pi_gemm_small_m_variant(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M,
+                                      int N, int K, int variant, cudaStream_t stream) {
+    return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
 }

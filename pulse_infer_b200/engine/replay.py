@@ -42,6 +42,8 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, dev
         segments = []
         for entry in obj.get("entries", []):
             rid = entry["id"]
+            if not entry.get("tokens"):
+                continue                      # an entry without tokens asks for nothing
             if not runner.cache.has(rid):
                 runner.open(rid)
             segments.append(Segment(rid, [int(t) for t in entry["tokens"]], [int(w) for w in entry.get("want", [])]))

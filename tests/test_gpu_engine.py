@@ -191,6 +191,29 @@ def test_against_reference_golden(dtype, model_folders):
             i += 1
 
 
+def test_weights_stored_in_32bit_stay_32bit_in_bfloat16_mode(model_folders, plain_cache, tmp_path):
+    """A folder whose tensors are stored as F32: in bfloat16 mode they stay 32-bit (products with them run
+    in 32-bit), in float32 mode nothing changes; both match the plain implementation."""
+    import shutil
+    from pulse_infer_b200.engine import Segment
+    from pulse_infer_b200.weights import SafetensorsFile, write_safetensors
+    need_gpu()
+    src = model_folders["A"]
+    folder = str(tmp_path / "f32")
+    shutil.copytree(src, folder)
+    f = SafetensorsFile(os.path.join(src, "model.safetensors"))
+    write_safetensors(os.path.join(folder, "model.safetensors"), {n: f.tensor(n).float() for n in f.names()})
+    toks = random_tokens(9, 50, CONFIGS["A"].vocab_size)
+    want = _plain(plain_cache, src, toks)
+    for dtype in ("bfloat16", "float32"):
+        runner = _runner(folder, dtype)
+        assert runner.model.layers[0].mixer.qkv.dtype == torch.float32
+        runner.open("x")
+        got = torch.cat([runner.step([Segment("x", toks[:37], list(range(37)))]),
+                         runner.step([Segment("x", toks[37:], list(range(13)))])])
+        _check(got, want, dtype, f"F32 storage, {dtype} mode")
+
+
 def test_step_refuses_bad_batches(model_folders):
     from pulse_infer_b200.cache import CacheError, OutOfPages
     from pulse_infer_b200.engine import Segment, StepError
