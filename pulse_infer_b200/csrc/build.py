@@ -27,6 +27,7 @@ SOURCES = {
     "elementwise": "elementwise.cu",
     "gemm_f32": "gemm_f32.cu",
     "gemm_small_m": "gemm_small_m.cu",
+    "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_simple": "attention_simple.cu",
     "sampling": "sampling.cu",
 }

@@ -327,6 +327,45 @@ def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, 
     return out
 
 
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, gated: bool = False,
+                 out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """x bf16 [M, K], weight bf16 [N, K] -> [M, N] on tcgen05 tensor cores (TMEM accumulators, TMA loads).
+    ``gated``: weight rows are gate/up features interleaved in blocks of 16 (see ``interleave_gate_up``) and the
+    result is silu(gate) * up, [M, N / 2] bf16."""
+    _need_cuda(x, weight)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise KernelError("gemm_tcgen05 takes bfloat16 operands")
+    if x.stride(-1) != 1 or weight.stride(-1) != 1:
+        raise KernelError("gemm_tcgen05 needs unit stride along k")
+    M, K = x.shape
+    N, K2 = weight.shape
+    if K != K2:
+        raise KernelError(f"inner sizes differ: {K} vs {K2}")
+    if out is None:
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    lib = _lib("gemm_tcgen05")
+    _check(lib, lib.pi_gemm_tcgen05(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
+                                    c_int(_code(out.dtype)), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
+                                    c_int(1 if gated else 0), c_int(max_ctas), _stream()), "gemm_tcgen05")
+    return out
+
+
+def gemm_tcgen05_status() -> int:
+    """0 if every bounded wait of the tcgen05 kernels launched so far was met (synchronises the device)."""
+    lib = _lib("gemm_tcgen05")
+    status = ctypes.c_uint(0)
+    _check(lib, lib.pi_gemm_tcgen05_status(ctypes.byref(status)), "gemm_tcgen05_status", launches=0)
+    return int(status.value)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up weights -> [2I, K] with rows in blocks of 32: 16 gate rows, then their 16 up rows."""
+    I, K = gate.shape
+    if I % 16:
+        raise KernelError("the interleaved layout needs an intermediate size that is a multiple of 16")
+    return torch.stack([gate.view(I // 16, 16, K), up.view(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """y = x W^T with W [out, in] (src/layer/linear.cpp:213).  A bfloat16 weight runs on tensor cores with
     32-bit accumulation: up to SMALL_M_ROWS rows on the weight-streaming kernel, more on cuBLAS.  A float32

@@ -263,6 +263,38 @@ def test_gemm_small_m(M, N, K, out_dtype):
         assert torch.equal(one[0], out[M - 1])
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 256, 128), (300, 515, 200), (257, 1000, 4096), (2048, 1024, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(M, N, K, out_dtype):
+    """The tcgen05 / TMEM / TMA product against a float64 product; every bounded wait must have been met."""
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(M + N + K)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.5).to(torch.bfloat16)
+    out = ops.gemm_tcgen05(x.to(dev), w.to(dev), out_dtype).cpu()
+    assert ops.gemm_tcgen05_status() == 0
+    want = x.double() @ w.double().t()
+    scale = float(want.abs().max())
+    assert float((out.double() - want).abs().max()) <= (1e-5 if out_dtype == torch.float32 else 2 ** -8) * scale + 1e-6
+    # fewer CTAs than tiles: the persistent loop and both accumulator buffers are exercised
+    again = ops.gemm_tcgen05(x.to(dev), w.to(dev), out_dtype, max_ctas=3).cpu()
+    assert ops.gemm_tcgen05_status() == 0 and torch.equal(again, out)
+
+
+def test_gemm_tcgen05_gated_epilogue():
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(5)
+    M, I, K = 200, 224, 192
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    gate = (torch.randn(I, K, generator=g) * 0.3).to(torch.bfloat16)
+    up = (torch.randn(I, K, generator=g) * 0.3).to(torch.bfloat16)
+    w = ops.interleave_gate_up(gate.to(dev), up.to(dev))
+    out = ops.gemm_tcgen05(x.to(dev), w, torch.bfloat16, gated=True).cpu()
+    assert ops.gemm_tcgen05_status() == 0 and out.shape == (M, I)
+    want = plain_model.silu((x.double() @ gate.double().t()).numpy()) * (x.double() @ up.double().t()).numpy()
+    assert np.abs(out.double().numpy() - want).max() <= 2 ** -7 * np.abs(want).max()
+
+
 def test_linear_bfloat16_and_mixed():
     dev, ops = need_gpu(), _ops()
     g = torch.Generator().manual_seed(0)
