@@ -125,6 +125,47 @@ struct TcParams {
     int tiles_m, tiles_n;
 };
 
+// One 32-column chunk of an accumulator row goes to memory: plain (bf16 or f32), or through the gated activation.
+__device__ __forceinline__ void tc_store_chunk(const TcParams& p, int row, int col0, const float (&v)[32]) {
+    if (p.gated) {
+        // columns come in blocks of 32: 16 gate features followed by their 16 up features;
+        // out[row, col0 / 2 + j] = silu(gate_j) * up_j  (out has N / 2 columns)
+        const int col = col0 / 2;
+        bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + col;
+        alignas(16) bf16 packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float g = v[j], u = v[16 + j];
+            packed[j] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+        }
+        if (col + 16 <= p.N / 2 && (p.ldo & 7) == 0) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(packed);
+            *reinterpret_cast<uint4*>(dst + 8) = *reinterpret_cast<const uint4*>(packed + 8);
+        } else {
+            for (int j = 0; j < 16 && col + j < p.N / 2; ++j) dst[j] = packed[j];
+        }
+    } else if (p.out_f32) {
+        float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
+        if (col0 + 32 <= p.N && (p.ldo & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+        }
+    } else {
+        bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + col0;
+        alignas(16) bf16 packed[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) packed[j] = __float2bfloat16_rn(v[j]);
+        if (col0 + 32 <= p.N && (p.ldo & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(packed + j);
+        } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = packed[j];
+        }
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const TcParams p) {
@@ -217,45 +258,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             for (int c = 0; c < BN; c += 32) {
                 float v[32];
                 tmem_ld32(taddr + c, v);
-                if (row < p.M) {
-                    if (p.gated) {
-                        // columns come in blocks of 32: 16 gate features followed by their 16 up features;
-                        // out[row, (n0 + c) / 2 + j] = silu(gate_j) * up_j  (out has N / 2 columns)
-                        const int col = (n0 + c) / 2;
-                        bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + col;
-                        alignas(16) bf16 packed[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float g = v[j], u = v[16 + j];
-                            packed[j] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-                        }
-                        if (col + 16 <= p.N / 2) {
-                            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(packed);
-                            *reinterpret_cast<uint4*>(dst + 8) = *reinterpret_cast<const uint4*>(packed + 8);
-                        } else {
-                            for (int j = 0; j < 16 && col + j < p.N / 2; ++j) dst[j] = packed[j];
-                        }
-                    } else if (p.out_f32) {
-                        float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + n0 + c;
-                        if (n0 + c + 32 <= p.N && (p.ldo & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-                            for (int j = 0; j < 32 && n0 + c + j < p.N; ++j) dst[j] = v[j];
-                        }
-                    } else {
-                        bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + n0 + c;
-                        alignas(16) bf16 packed[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) packed[j] = __float2bfloat16_rn(v[j]);
-                        if (n0 + c + 32 <= p.N && (p.ldo & 7) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(packed + j);
-                        } else {
-                            for (int j = 0; j < 32 && n0 + c + j < p.N; ++j) dst[j] = packed[j];
-                        }
-                    }
-                }
+                if (row < p.M) tc_store_chunk(p, row, n0 + c, v);
             }
             tc_fence_before();
             __syncwarp();
@@ -269,6 +272,180 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The same product on CTA pairs (cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile.  Each CTA
+// loads its own 128 rows of x and its own half (128 rows) of the W tile; one thread of the pair's first CTA
+// issues tcgen05.mma.cta_group::2 (M 256), which reads both CTAs' shared memory and writes rows 0-127 of the
+// tile into its own TMEM and rows 128-255 into the peer's.  Per CTA that is 32 KB of operands per 64-wide k
+// step instead of 48 KB for the same tensor-core work.  No multicast loads are used: readiness of the peer's
+// stage reaches the first CTA by a forwarding thread (wait on the own barrier, remote arrive on the leader's).
+// tcgen05.commit multicasts "stage free" and "tile complete" to both CTAs.
+// Threads: warp 0 TMA, warp 1 MMA (leader only) + TMEM, warps 2-5 epilogue, warp 6 forwarder (peer only).
+// ---------------------------------------------------------------------------------------------------
+#define TC2_THREADS 192
+
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(void* bar, unsigned cta) {   // arrive on the same barrier of CTA `cta`
+    unsigned raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(bar)), "r"(cta));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(raddr) : "memory");
+}
+__device__ __forceinline__ unsigned mapa_u32(void* ptr, unsigned cta) {
+    unsigned raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(ptr)), "r"(cta));
+    return raddr;
+}
+// TMA load into this CTA's shared memory whose completion bytes are reported to a barrier of the CTA pair
+// (given as a shared::cluster address, here the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, unsigned bar_cluster_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(void* dst_smem, unsigned cols) {    // one warp in each CTA of the pair
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                           unsigned accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma2_commit_both(void* bar) {   // arrives on `bar` in both CTAs of the pair
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(TC2_THREADS, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const TcParams p) {
+    constexpr int BN = 256, HALF = 128;
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = HALF * TC_BK * 2;
+    constexpr unsigned TMEM_COLS = 2 * BN;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;                                    // [STAGES][128 x 64 bf16] this CTA's rows of x
+    unsigned char* sB = smem + STAGES * A_BYTES;                 // [STAGES][128 x 64 bf16] this CTA's half of the W tile
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sB + STAGES * B_BYTES);
+    unsigned long long* full = bars;                             // [STAGES] leader only: both CTAs' loads of the stage landed
+    unsigned long long* peer_full = bars + STAGES;               // [STAGES] unused (kept so that both kernels share a layout)
+    unsigned long long* empty = bars + 2 * STAGES;               // [STAGES] MMA (multicast) -> both producers
+    unsigned long long* acc_full = bars + 3 * STAGES;            // [2] MMA (multicast) -> both epilogues
+    unsigned long long* acc_empty = bars + 3 * STAGES + 2;       // [2] leader only: 8 epilogue warps of the pair
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 3 * STAGES + 4);
+    volatile unsigned* failed = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_rank();                        // 0: leader (issues the MMAs), 1: peer
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&peer_full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc2(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                          // both CTAs' barriers exist before anyone signals them
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    const int pairs = gridDim.x / 2, pair = blockIdx.x / 2;
+    const int num_tiles = p.tiles_m * p.tiles_n;                 // tiles of 256 x 256
+    const int k_tiles = (p.K + TC_BK - 1) / TC_BK;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            unsigned it = 0;
+            for (int tile = pair; tile < num_tiles && !*failed; tile += pairs) {
+                const int m0 = (tile % p.tiles_m) * 256 + (int)rank * TC_BM, n0 = (tile / p.tiles_m) * BN + (int)rank * HALF;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const unsigned s = it % STAGES, round = it / STAGES;
+                    if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, (1u << 24) | it, failed)) break;
+                    if (rank == 0) {
+                        mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));      // this CTA's bytes and the peer's
+                        tma_load_2d(sA + s * A_BYTES, &map_x, kt * TC_BK, m0, &full[s]);
+                        tma_load_2d(sB + s * B_BYTES, &map_w, kt * TC_BK, n0, &full[s]);
+                    } else {
+                        const unsigned leader_full = mapa_u32(&full[s], 0);
+                        tma_load_2d_pair(sA + s * A_BYTES, &map_x, kt * TC_BK, m0, leader_full);
+                        tma_load_2d_pair(sB + s * B_BYTES, &map_w, kt * TC_BK, n0, leader_full);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+            unsigned it = 0, local = 0;
+            for (int tile = pair; tile < num_tiles && !*failed; tile += pairs, ++local) {
+                const unsigned a = local & 1, use = local >> 1;
+                if (use > 0 && !mbar_wait(&acc_empty[a], (use - 1) & 1, (2u << 24) | local, failed)) break;
+                tc_fence_after();
+                const unsigned tmem_d = tmem_base + a * BN;
+                bool ok = true;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const unsigned s = it % STAGES, round = it / STAGES;
+                    if (!mbar_wait(&full[s], round & 1, (3u << 24) | it, failed)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma2_bf16(tmem_d, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
+                                   (kt > 0 || k > 0) ? 1u : 0u);
+                    umma2_commit_both(&empty[s]);
+                }
+                if (!ok) break;
+                umma2_commit_both(&acc_full[a]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        unsigned local = 0;
+        for (int tile = pair; tile < num_tiles && !*failed; tile += pairs, ++local) {
+            const unsigned a = local & 1, use = local >> 1;
+            if (!mbar_wait(&acc_full[a], use & 1, (4u << 24) | local, failed)) break;
+            tc_fence_after();
+            const int m0 = (tile % p.tiles_m) * 256 + (int)rank * TC_BM, n0 = (tile / p.tiles_m) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            const unsigned taddr = tmem_base + a * BN + ((unsigned)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_ld32(taddr + c, v);
+                if (row < p.M) tc_store_chunk(p, row, n0 + c, v);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(&acc_empty[a]);
+                else mbar_arrive_remote(&acc_empty[a], 0);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();          // nobody frees TMEM or leaves while the pair may still touch its memory or barriers
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, TMEM_COLS);
     }
 }
 
@@ -317,6 +494,35 @@ static int tc_launch(const CUtensorMap& mx, const CUtensorMap& mw, const TcParam
     return pi_check_launch("pi_gemm_tcgen05");
 }
 
+template <int STAGES>
+static int tc_launch_2cta(const CUtensorMap& mx, const CUtensorMap& mw, const TcParams& p, int pairs, cudaStream_t stream) {
+    static bool configured = false;
+    const size_t smem = (size_t)STAGES * (TC_BM + 128) * TC_BK * 2 + (3 * STAGES + 4) * 8 + 16 + 1024;
+    auto kernel = gemm_tcgen05_2cta_kernel<STAGES>;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) {
+            snprintf(g_pi_error, sizeof(g_pi_error), "pi_gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+            return (int)err;
+        }
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(TC2_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, mx, mw, p);
+    return pi_check_launch("pi_gemm_tcgen05 (CTA pairs)");
+}
+
 // Reads and clears the status word of the last launches (synchronises the device).  0 means every wait was met.
 PI_EXPORT int pi_gemm_tcgen05_status(unsigned* status) {
     unsigned zero = 0;
@@ -331,8 +537,9 @@ PI_EXPORT int pi_gemm_tcgen05_status(unsigned* status) {
 
 // gated = 1: W holds gate and up rows interleaved in blocks of 16 (rows 32b .. 32b+15 gate features 16b .. 16b+15,
 // rows 32b+16 .. 32b+31 the matching up features); out is [M, N / 2] bf16 = silu(gate) * up.
+// mode 0: CTA pairs when M > 128, single CTAs otherwise; 1: single CTAs; 2: CTA pairs
 PI_EXPORT int pi_gemm_tcgen05(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                              int K, int gated, int max_ctas, cudaStream_t stream) {
+                              int K, int gated, int max_ctas, int mode, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
         return pi_refuse("pi_gemm_tcgen05: K=%d and the leading dimensions (%d, %d) must be positive multiples of 8", K, ldx, ldw);
@@ -340,13 +547,22 @@ PI_EXPORT int pi_gemm_tcgen05(const void* x, int ldx, const void* W, int ldw, vo
     if (out_dtype != PI_F32 && out_dtype != PI_BF16) return pi_refuse("pi_gemm_tcgen05: unknown output dtype code %d", out_dtype);
     if (gated && (out_dtype != PI_BF16 || N % 32 != 0)) return pi_refuse("pi_gemm_tcgen05: the gated epilogue needs bf16 output and N %% 32 == 0 (N=%d)", N);
     const int BN = 256;
+    const bool pairs_mode = mode == 2 || (mode == 0 && M > TC_BM);
     CUtensorMap mx, mw;
     int rc = tc_make_map(&mx, x, M, K, ldx, TC_BM);
     if (rc) return rc;
-    rc = tc_make_map(&mw, W, N, K, ldw, BN);
+    rc = tc_make_map(&mw, W, N, K, ldw, pairs_mode ? 128 : BN);
     if (rc) return rc;
     TcParams p;
     p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = out_dtype == PI_F32; p.gated = gated;
+    if (pairs_mode) {
+        p.tiles_m = (M + 255) / 256;
+        p.tiles_n = (N + BN - 1) / BN;
+        int pairs = p.tiles_m * p.tiles_n;
+        const int limit = (max_ctas > 0 ? max_ctas : 148) / 2;
+        if (pairs > limit) pairs = limit > 0 ? limit : 1;
+        return tc_launch_2cta<6>(mx, mw, p, pairs, stream);
+    }
     p.tiles_m = (M + TC_BM - 1) / TC_BM;
     p.tiles_n = (N + BN - 1) / BN;
     int ctas = p.tiles_m * p.tiles_n;

@@ -328,10 +328,10 @@ def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, 
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, gated: bool = False,
-                 out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+                 out: torch.Tensor | None = None, max_ctas: int = 0, mode: int = 0) -> torch.Tensor:
     """x bf16 [M, K], weight bf16 [N, K] -> [M, N] on tcgen05 tensor cores (TMEM accumulators, TMA loads).
     ``gated``: weight rows are gate/up features interleaved in blocks of 16 (see ``interleave_gate_up``) and the
-    result is silu(gate) * up, [M, N / 2] bf16."""
+    result is silu(gate) * up, [M, N / 2] bf16.  ``mode``: 0 chosen from M, 1 single CTAs, 2 CTA pairs."""
     _need_cuda(x, weight)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError("gemm_tcgen05 takes bfloat16 operands")
@@ -346,7 +346,7 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype =
     lib = _lib("gemm_tcgen05")
     _check(lib, lib.pi_gemm_tcgen05(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
                                     c_int(_code(out.dtype)), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
-                                    c_int(1 if gated else 0), c_int(max_ctas), _stream()), "gemm_tcgen05")
+                                    c_int(1 if gated else 0), c_int(max_ctas), c_int(mode), _stream()), "gemm_tcgen05")
     return out
 
 
