@@ -196,10 +196,13 @@ PI_EXPORT int pi_add_rmsnorm(float* h, const void* delta, const void* weight, in
 }
 
 // ---------------------------------------------------------------------------------------------------
-// SiLU(gate) * up on the fused [n, 2*inter] output of the gate_up product: out[n, inter]
+// SiLU(gate) * up on the fused [n, 2*inter] output of the gate_up product: out[n, inter].
+// blocked = 0: columns are [all gate | all up].  blocked = 1: columns come in blocks of 32, 16 gate features
+// followed by their 16 up features (the layout the tcgen05 product's gated epilogue wants of the weight rows).
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, const Prefetch pf) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, int blocked,
+                                const Prefetch pf) {
     if (pi_prefetch_role(pf)) return;
     pdl_wait();
     pdl_trigger();
@@ -207,15 +210,17 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     if (e >= total) return;
     const size_t row = e / inter;
     const int col = (int)(e % inter);
-    const float g = to_float<T>(gu[row * 2 * (size_t)inter + col]);
-    const float u = to_float<T>(gu[row * 2 * (size_t)inter + inter + col]);
+    const int gcol = blocked ? (col / 16) * 32 + col % 16 : col;
+    const int ucol = blocked ? gcol + 16 : inter + col;
+    const float g = to_float<T>(gu[row * 2 * (size_t)inter + gcol]);
+    const float u = to_float<T>(gu[row * 2 * (size_t)inter + ucol]);
     out[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
 // 8 elements (bf16) or 4 (float) per thread with 16-byte accesses; needs inter % VEC == 0
 template <typename T, int VEC>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total_vecs,
-                                    const Prefetch pf) {
+                                    int blocked, const Prefetch pf) {
     struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
     if (pi_prefetch_role(pf)) return;
     pdl_wait();
@@ -225,8 +230,10 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
     const int vecs_per_row = inter / VEC;
     const size_t row = idx / vecs_per_row;
     const int col = (int)(idx % vecs_per_row) * VEC;
-    const Pack g = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + col);
-    const Pack u = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + inter + col);
+    const int gcol = blocked ? (col / 16) * 32 + col % 16 : col;     // VEC divides 16: a vector stays inside a block
+    const int ucol = blocked ? gcol + 16 : inter + col;
+    const Pack g = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + gcol);
+    const Pack u = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + ucol);
     Pack o;
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
@@ -236,10 +243,11 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
     *reinterpret_cast<Pack*>(out + row * (size_t)inter + col) = o;
 }
 
-PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, const void* prefetch_ptr,
+PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int inter, int blocked, const void* prefetch_ptr,
                           unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (inter <= 0) return pi_refuse("pi_silu_mul: inter=%d must be positive", inter);
+    if (blocked && inter % 16 != 0) return pi_refuse("pi_silu_mul: the blocked layout needs inter %% 16 == 0 (inter=%d)", inter);
     const size_t total = (size_t)n * inter;
     const int threads = 256;
     if (dtype == PI_BF16 && inter % 8 == 0) {
@@ -247,19 +255,19 @@ PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int 
         const unsigned own = (unsigned)((vecs + threads - 1) / threads);
         const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, (int)own);
         pi_launch(silu_mul_vec_kernel<bf16, 8>, dim3(own + pi_prefetch_ctas(pf)), dim3(threads), 0, stream,
-                  (const bf16*)gate_up, (bf16*)out, inter, vecs, pf);
+                  (const bf16*)gate_up, (bf16*)out, inter, vecs, blocked, pf);
     } else if (dtype == PI_F32 && inter % 4 == 0) {
         const size_t vecs = total / 4;
         const unsigned own = (unsigned)((vecs + threads - 1) / threads);
         const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, (int)own);
         pi_launch(silu_mul_vec_kernel<float, 4>, dim3(own + pi_prefetch_ctas(pf)), dim3(threads), 0, stream,
-                  (const float*)gate_up, (float*)out, inter, vecs, pf);
+                  (const float*)gate_up, (float*)out, inter, vecs, blocked, pf);
     } else if (dtype == PI_BF16 || dtype == PI_F32) {
         // widths that are no multiple of the vector: rows may start unaligned, so plain element accesses
         const unsigned blocks = (unsigned)((total + threads - 1) / threads);
         const Prefetch pf = pi_make_prefetch(prefetch_ptr, prefetch_bytes, (int)blocks);
-        if (dtype == PI_BF16) pi_launch(silu_mul_kernel<bf16>, dim3(blocks + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total, pf);
-        else pi_launch(silu_mul_kernel<float>, dim3(blocks + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total, pf);
+        if (dtype == PI_BF16) pi_launch(silu_mul_kernel<bf16>, dim3(blocks + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total, blocked, pf);
+        else pi_launch(silu_mul_kernel<float>, dim3(blocks + pi_prefetch_ctas(pf)), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total, blocked, pf);
     } else {
         return pi_refuse("pi_silu_mul: unknown dtype code %d", dtype);
     }

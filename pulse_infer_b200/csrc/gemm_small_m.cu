@@ -5,7 +5,8 @@
 // padded along the batch.  The few hundred kilobytes of x stay in L1/L2.
 //
 // A CTA owns 16 output features; its warps split K into contiguous ranges and their partial sums are added
-// in warp order through shared memory, so a result does not depend on the launch or on the other rows.
+// in warp order through shared memory, so a result does not depend on the other rows of the batch (for a given
+// launch shape; the shape, and with it the split of K, is chosen from M's bucket, N and K).
 // Wide outputs (thousands of 16-feature tiles) use 8 warps per CTA with two register sets of weights in
 // flight; narrow ones (N = 4096 gives only 256 tiles) use 16 warps per CTA so that the whole GPU still has
 // loads in flight.

@@ -98,3 +98,8 @@ class ModelRunner:
             bad = int(self._last_ctx.error_count.item())
             if bad:
                 raise StepError(f"{bad} key/value rows had no page to go to: block table and batch disagree")
+        if self.runtime.mode == "bfloat16":
+            from .. import ops
+            status = ops.gemm_tcgen05_status()
+            if status:
+                raise StepError(f"a wait inside the tcgen05 product ran out (status {status:#x})")

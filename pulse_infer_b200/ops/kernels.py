@@ -95,6 +95,9 @@ def preload(head_dims=(), simple_attention: bool = False, float32_products: bool
     _lib("elementwise")
     if float32_products:
         _lib("gemm_f32")
+    else:
+        _lib("gemm_small_m")
+        _lib("gemm_tcgen05")
     if simple_attention:
         _lib("attention_simple")
     for d in head_dims:
@@ -145,8 +148,10 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
 
 
 # ---- SiLU(gate) * up ------------------------------------------------------------------------------------
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, prefetch: torch.Tensor | None = None) -> torch.Tensor:
-    """gate_up [T, 2*I] (gate columns first) -> [T, I]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, prefetch: torch.Tensor | None = None,
+             blocked: bool = False) -> torch.Tensor:
+    """gate_up [T, 2*I] -> [T, I].  Columns are [all gate | all up], or with ``blocked`` blocks of 32:
+    16 gate features followed by their 16 up features."""
     _need_cuda(gate_up)
     _need_contig(gate_up=gate_up)
     T, two_i = gate_up.shape
@@ -157,7 +162,7 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, prefetch: t
         out = torch.empty((T, inter), dtype=gate_up.dtype, device=gate_up.device)
     lib = _lib("elementwise")
     _check(lib, lib.pi_silu_mul(_p(gate_up), _p(out), c_int(_code(gate_up.dtype)), c_int(T), c_int(inter),
-                                *_prefetch_args(prefetch), _stream()), "silu_mul")
+                                c_int(1 if blocked else 0), *_prefetch_args(prefetch), _stream()), "silu_mul")
     return out
 
 

@@ -53,7 +53,7 @@ def test_add_rmsnorm(hidden, act, wdt):
     assert np.abs(xr.double().numpy() - want[rows.long().numpy()]).max() <= tol * np.abs(want).max()
 
 
-@pytest.mark.parametrize("inter", [12288, 222, 7])
+@pytest.mark.parametrize("inter", [12288, 222, 7, 224])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_silu_mul(inter, dtype):
     dev, ops = need_gpu(), _ops()
@@ -63,6 +63,10 @@ def test_silu_mul(inter, dtype):
     want = plain_model.silu(g) * u
     tol = 1e-6 if dtype == torch.float32 else 2 ** -8
     assert np.abs(out - want).max() <= tol * max(1.0, np.abs(want).max())
+    if inter % 16 == 0:      # the same values with gate and up columns interleaved in blocks of 16
+        blocked = torch.stack([gu[:, :inter].view(5, inter // 16, 16), gu[:, inter:].view(5, inter // 16, 16)], dim=2)
+        out_b = ops.silu_mul(blocked.reshape(5, 2 * inter).contiguous().to(dev), blocked=True).cpu().double().numpy()
+        assert np.array_equal(out_b, out)
 
 
 def test_rope_table_large_positions():
@@ -257,10 +261,14 @@ def test_gemm_small_m(M, N, K, out_dtype):
     err = float((out.double() - want).abs().max())
     scale = float(want.abs().max())
     assert err <= (2e-5 if out_dtype == torch.float32 else 2 ** -8) * scale + 1e-6
-    # a row's result does not depend on the rows around it
+    # a row's result does not depend on the rows around it: bitwise while the launch shape is the same (up to 8
+    # rows here), to rounding when more rows pick another split of K
     if M > 1:
         one = ops.gemm_small_m(x[M - 1:].contiguous().to(dev), w.to(dev), out_dtype).cpu()
-        assert torch.equal(one[0], out[M - 1])
+        if M <= 8:
+            assert torch.equal(one[0], out[M - 1])
+        else:
+            assert float((one[0].double() - out[M - 1].double()).abs().max()) <= 2 ** -7 * scale
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 256, 128), (300, 515, 200), (257, 1000, 4096), (2048, 1024, 1024)])
