@@ -1,0 +1,591 @@
+// Paged flash attention for prompt portions on the 5th-generation tensor cores (bfloat16).
+//
+// A CTA owns 128 query rows - (token, head-in-group) pairs of one kv head of one request segment, as in
+// attention_mma.cu - and walks the visible keys in tiles of 128:
+//   S = Q K^T      tcgen05.mma, M 128 x N 128, both operands K-major from 128-byte-swizzled shared memory,
+//                  accumulator in TMEM; two S buffers so the next tile's scores are computed while the
+//                  current tile is in the softmax
+//   softmax        four warps, ONE THREAD PER ROW: the row's 128 scores come out of TMEM with tcgen05.ld, so
+//                  max / exp2 / sum need no shuffles; probabilities go to shared memory as bf16 in the
+//                  swizzled K-major layout; the running output in TMEM is rescaled in place (tcgen05.ld/st)
+//                  only when a row's maximum moved
+//   O += P V       tcgen05.mma, A = P from shared memory, B = V tile used MN-major (rows of V are keys)
+// Keys and values arrive by TMA, one box per (page, 64-wide half of the head): cp.async.bulk.tensor.2d over
+// the page pool seen as a [pages * kv heads * page size, head size] matrix; the page ids come from the block
+// table.  Roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5 softmax / output.
+// Every mbarrier wait is bounded; on a timeout the kernel records a code, all roles fall through, TMEM is freed.
+//
+// Needs: head size 64 or 128 (PI_HEAD_DIM), page size in {8, 16, 32, 64, 128}.  Segments of one token are
+// left to the decode kernel.
+//
+// Reference parity: src/ops/kernels/cuda/paged_attention.cu:65-137 (grouping, 1/sqrt(d) scale, causal bound
+// by absolute position, online softmax, out = acc / sum).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <math.h>
+
+#include "common.cuh"
+
+#ifndef PI_HEAD_DIM
+#error "compile with -DPI_HEAD_DIM=64 or 128"
+#endif
+
+#if PI_HEAD_DIM == 64 || PI_HEAD_DIM == 128
+
+#define FA_BM 128            // rows of a query tile
+#define FA_ROWS 256          // rows of a CTA: two query tiles
+#define FA_BN 128            // keys of a tile
+#define FA_STAGES 5          // ring of K / V tiles
+#define FA_THREADS 320
+#define FA_SPIN_LIMIT (1u << 22)
+
+__device__ unsigned g_fa_status;
+
+// -DFA_PROFILE: the first CTA adds the cycles it spends at each wait and in each phase to g_fa_prof
+#ifdef FA_PROFILE
+__device__ unsigned long long g_fa_prof[16];
+#define FA_T0() long long fa_t0 = clock64()
+#define FA_ACC(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { long long t = clock64(); atomicAdd(&g_fa_prof[i], (unsigned long long)(t - fa_t0)); fa_t0 = t; } } while (0)
+#else
+#define FA_T0() do {} while (0)
+#define FA_ACC(i) do {} while (0)
+#endif
+
+struct FaParams {
+    const bf16* q; int q_stride;
+    const int* block_table; int bt_stride;
+    const int* seg_off; const int* seg_slot; const int* seg_start; const int* seg_len;
+    bf16* out;
+    int nq, nkv, group;
+    int page_size, window;
+    float scale_log2;
+    int tiles_per_seg, num_segments;
+};
+
+// ---- PTX wrappers (see gemm_tcgen05.cu for the same set with comments) ------------------------------------
+__device__ __forceinline__ unsigned fa_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void fa_mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(fa_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void fa_mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fa_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fa_mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fa_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool fa_mbar_wait(void* bar, unsigned parity, unsigned code, volatile unsigned* failed) {
+    for (unsigned spin = 0; spin < FA_SPIN_LIMIT; ++spin) {
+        unsigned ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(fa_smem(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spin & 1023u) == 1023u && *failed) return false;
+    }
+    *failed = 1;
+    atomicCAS(&g_fa_status, 0u, code);
+    return false;
+}
+__device__ __forceinline__ void fa_tma_load(void* dst, const CUtensorMap* map, int c0, int c1, void* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(fa_smem(dst)), "l"(map), "r"(fa_smem(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fa_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                       unsigned accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// A operand from tensor memory (rows = lanes, two bf16 per 32-bit column), B from shared memory
+__device__ __forceinline__ void fa_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void fa_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(fa_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void fa_tmem_ld32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fa_tmem_st32(unsigned taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void fa_tmem_st16(unsigned taddr, const unsigned (&w)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "r"(w[8]), "r"(w[9]),
+          "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15])
+        : "memory");
+}
+
+// K-major operand tile: rows of 128 bytes (64 bf16), 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ unsigned long long fa_desc_kmajor(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// MN-major operand (V as the B operand of P V: its rows are keys = the k index, the head dimension is
+// contiguous): 128-byte swizzle, blocks of 64 elements along the head dimension `lbo` bytes apart,
+// groups of 8 keys 1024 bytes apart
+__device__ __forceinline__ unsigned long long fa_desc_mnmajor(unsigned addr, unsigned lbo) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ float fa_ex2(float x) {   // 2^x; -inf gives 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ int fa_window_lo(int pos, int window) {
+    return (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+}
+
+// One pass of a row over a 128-key tile of scores in TMEM.  MASKED: keys outside [lo_r, pos_r] or at / beyond
+// kend count as -inf.  Pass 1 returns the row's maximum of the raw scores.
+template <bool MASKED>
+__device__ __forceinline__ float fa_row_max(unsigned tmem_row, int k0, int pos_r, int lo_r, int kend) {
+    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < FA_BN; c += 32) {
+        float v[32];
+        fa_tmem_ld32(tmem_row + c, v);
+        if (MASKED) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int key = k0 + c + i;
+                if (!(key <= pos_r && key >= lo_r && key < kend)) v[i] = -INFINITY;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            m0 = fmaxf(m0, v[i]); m1 = fmaxf(m1, v[i + 1]); m2 = fmaxf(m2, v[i + 2]); m3 = fmaxf(m3, v[i + 3]);
+        }
+    }
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// Pass 2: p = 2^(s * scale - base) as bf16, two to a 32-bit column, written over the row's own scores (the 32
+// scores of a chunk are read before the 16 columns that replace scores already read are written); returns
+// the row's sum.
+template <bool MASKED>
+__device__ __forceinline__ float fa_row_probs(unsigned tmem_row, float scale_log2, float base, int k0, int pos_r, int lo_r, int kend) {
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    const float nbase = -base;
+#pragma unroll 1
+    for (int c = 0; c < FA_BN; c += 32) {
+        float v[32];
+        fa_tmem_ld32(tmem_row + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float pv = fa_ex2(fmaf(v[i], scale_log2, nbase));
+            if (MASKED) {
+                const int key = k0 + c + i;
+                if (!(key <= pos_r && key >= lo_r && key < kend)) pv = 0.0f;
+            }
+            v[i] = pv;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) { s0 += v[i]; s1 += v[i + 1]; s2 += v[i + 2]; s3 += v[i + 3]; }
+        unsigned w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);     // the even key in the low half
+            w[i] = *reinterpret_cast<unsigned*>(&t);
+        }
+        fa_tmem_st16(tmem_row + c / 2, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    return (s0 + s1) + (s2 + s3);
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+    constexpr int HALVES = D / 64;                       // 64-wide (128-byte) column blocks of the head
+    constexpr unsigned HALF_BYTES = 128 * 128;           // 128 rows x 128 bytes
+    constexpr unsigned TILE_BYTES = HALVES * HALF_BYTES; // a Q, K or V tile: 128 rows x D bf16
+    constexpr unsigned TMEM_COLS = 512;
+    constexpr unsigned S_COL = 0, O_COL = 256;           // S of query tile x at S_COL + 128 x (P over its first 64 columns), O at O_COL + 128 x
+
+    // ---- which rows -------------------------------------------------------------------------------------
+    const int kvh = blockIdx.x % p.nkv;
+    const int rest = blockIdx.x / p.nkv;
+    const int tile = p.tiles_per_seg - 1 - rest / p.num_segments;     // tiles with the most keys first
+    const int seg = rest % p.num_segments;
+    const int len = p.seg_len[seg];
+    if (len == 1) return;                                 // single tokens go to the decode kernel
+    const int G = p.group;
+    const int rows_total = len * G;
+    const int row0 = tile * FA_ROWS;
+    if (row0 >= rows_total) return;
+    const bool two = row0 + FA_BM < rows_total;           // the second query tile has rows
+    const int start = p.seg_start[seg], tok_off = p.seg_off[seg];
+    const int* table = p.block_table + (size_t)p.seg_slot[seg] * p.bt_stride;
+    const int row_last = min(row0 + FA_ROWS, rows_total) - 1;
+    const int pos_first = start + row0 / G, pos_last = start + row_last / G;
+    const int kbegin = (fa_window_lo(pos_first, p.window) / FA_BN) * FA_BN;
+    const int kend = pos_last + 1;
+    const int num_tiles = (kend - kbegin + FA_BN - 1) / FA_BN;
+
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = smem;                             // [2 query tiles][HALVES][128 rows][128 B]
+    unsigned char* sKV = sQ + 2 * TILE_BYTES;             // [FA_STAGES][HALVES][128 keys][128 B]: K0 V0 K1 V1 ... in a ring
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sKV + FA_STAGES * TILE_BYTES);
+    unsigned long long* full = bars;                      // [FA_STAGES] TMA -> MMA: the tile of a stage has landed
+    unsigned long long* empty = bars + FA_STAGES;         // [FA_STAGES] MMA -> TMA: the products that read it are done
+    unsigned long long* s_full = bars + 2 * FA_STAGES;    // [2] MMA -> softmax of query tile x: scores are in TMEM
+    unsigned long long* p_ready = s_full + 2;             // [2] softmax (4 warps) -> MMA: P written, O rescaled, S read
+    unsigned long long* pv_done = s_full + 4;             // [2] MMA -> softmax: O updated, P free
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(s_full + 6);
+    volatile unsigned* failed = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < FA_STAGES; ++i) { fa_mbar_init(&full[i], 1); fa_mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { fa_mbar_init(&s_full[i], 1); fa_mbar_init(&p_ready[i], 4); fa_mbar_init(&pv_done[i], 1); }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pdl_wait();   // q and the pages are written by the kernels before this one
+
+    // the ring starts as zeros: rows of a value tile that no page fills must not hold NaN bit patterns (0 x NaN)
+    for (unsigned i = threadIdx.x; i < FA_STAGES * TILE_BYTES / 16; i += FA_THREADS) reinterpret_cast<uint4*>(sKV)[i] = make_uint4(0, 0, 0, 0);
+    // Q: thread r of the softmax warps copies row r into the swizzled K-major layout (16-byte chunk c of a
+    // 128-byte row goes to chunk c ^ (row & 7))
+    if (warp >= 2) {
+        const int r = (warp - 2) * 32 + lane;             // 0..255
+        const int rf = row0 + r;
+        const bool valid = rf < rows_total;
+        const bf16* src = p.q + (size_t)(tok_off + (valid ? rf / G : 0)) * p.q_stride + (size_t)(kvh * G + (valid ? rf % G : 0)) * D;
+        unsigned char* dst = sQ + (r >> 7) * TILE_BYTES + (r & 127) * 128;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const uint4 v = valid ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0, 0, 0, 0);
+            const int half = c / 8, cc = c % 8;
+            *reinterpret_cast<uint4*>(dst + half * HALF_BYTES + ((cc ^ (r & 7)) << 4)) = v;
+        }
+    }
+    fa_fence_async_smem();        // generic-proxy writes above become visible to TMA / tcgen05.mma
+    fa_fence_before();
+    __syncthreads();
+    fa_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: lane = page of the key tile ----------------
+        // Loads run K(0) V(0) K(1) V(1) ... through the ring.  The lanes look their pages up in the block
+        // table together (the lookups are the long latency here) and each issues the boxes of its own page.
+        const int ps = p.page_size, pages_per_tile = FA_BN / ps;
+        const unsigned page_bytes = (unsigned)ps * 128u;            // one (page, half) box
+        auto lookup = [&](int j) -> int {
+            const int key = kbegin + j * FA_BN + lane * ps;
+            return (j < num_tiles && lane < pages_per_tile && key < kend) ? table[key / ps] : -1;
+        };
+        int page = lookup(0);
+        for (int j = 0; j < num_tiles && !*failed; ++j) {
+            const int next_page = lookup(j + 1);
+            const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
+            const unsigned bytes = (unsigned)__popc(mask) * page_bytes * HALVES;
+            const int row = (page * p.nkv + kvh) * ps;
+            bool ok = true;
+#pragma unroll
+            for (int isv = 0; isv < 2; ++isv) {
+                const int n = 2 * j + isv, st = n % FA_STAGES, use = n / FA_STAGES;
+                FA_T0();
+                if (use > 0 && !fa_mbar_wait(&empty[st], (use - 1) & 1, (1u << 24) | n, failed)) { ok = false; break; }
+                FA_ACC(isv);
+                if (lane == 0) fa_mbar_expect_tx(&full[st], bytes);
+                __syncwarp();
+                if (page >= 0) {
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        fa_tma_load(sKV + st * TILE_BYTES + h * HALF_BYTES + lane * page_bytes, isv ? &map_v : &map_k, h * 64, row, &full[st]);
+                }
+            }
+            if (!ok) break;
+            page = next_page;
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // bf16 x bf16 -> f32, M 128; S: N 128, both K-major; PV: N D, B MN-major
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(FA_BN >> 3) << 17) | ((unsigned)(FA_BM >> 4) << 24);
+            const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) | ((unsigned)(FA_BM >> 4) << 24);
+            const int nx = two ? 2 : 1;
+            auto wait_full = [&](int n) -> bool { return fa_mbar_wait(&full[n % FA_STAGES], (n / FA_STAGES) & 1, (2u << 24) | n, failed); };
+            auto issue_s = [&](int x, int j) {     // S_x(j) = Q_x K(j)^T
+                const unsigned char* kt = sKV + ((2 * j) % FA_STAGES) * TILE_BYTES;
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        fa_mma(tmem_base + S_COL + x * 128, fa_desc_kmajor(fa_smem(sQ + x * TILE_BYTES + h * HALF_BYTES) + k * 32),
+                               fa_desc_kmajor(fa_smem(kt + h * HALF_BYTES) + k * 32), idesc_s, (h > 0 || k > 0) ? 1u : 0u);
+                fa_commit(&s_full[x]);
+            };
+            bool ok = wait_full(0);
+            if (ok) {
+                fa_fence_after();
+                for (int x = 0; x < nx; ++x) issue_s(x, 0);
+                fa_commit(&empty[0]);                                  // K(0) is no longer read
+            }
+            for (int j = 0; j < num_tiles && ok && !*failed; ++j) {
+                const bool have_next = j + 1 < num_tiles;
+                FA_T0();
+                if (!wait_full(2 * j + 1)) break;                      // V(j)
+                FA_ACC(3);
+                if (have_next && !wait_full(2 * j + 2)) break;         // K(j + 1)
+                FA_ACC(4);
+                const unsigned char* vt = sKV + ((2 * j + 1) % FA_STAGES) * TILE_BYTES;
+                for (int x = 0; x < nx; ++x) {
+                    if (!fa_mbar_wait(&p_ready[x], j & 1, (4u << 24) | (x << 20) | j, failed)) { ok = false; break; }
+                    FA_ACC(5 + x);
+                    fa_fence_after();
+                    // O_x += P_x V: 8 steps of 16 keys, P from tensor memory (8 columns a step); then the next
+                    // scores of this query tile, which overwrite P_x: the tensor pipe runs its products in order
+#pragma unroll
+                    for (int kk = 0; kk < FA_BN / 16; ++kk)
+                        fa_mma_ts(tmem_base + O_COL + x * 128, tmem_base + S_COL + x * 128 + kk * 8,
+                                  fa_desc_mnmajor(fa_smem(vt) + kk * 16 * 128, HALF_BYTES), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    fa_commit(&pv_done[x]);
+                    if (have_next) issue_s(x, j + 1);
+                    FA_ACC(7);
+                }
+                if (!ok) break;
+                fa_commit(&empty[(2 * j + 1) % FA_STAGES]);            // V(j) is no longer read
+                if (have_next) fa_commit(&empty[(2 * j + 2) % FA_STAGES]);   // nor is K(j + 1)
+            }
+        }
+    } else {
+        // ---------------- softmax and output: thread = row; warps 2-5 query tile 0, warps 6-9 query tile 1 ----------------
+        const int x = (warp - 2) >> 2;
+        const int quarter = warp & 3;                      // TMEM lanes 32 * quarter .. + 31
+        const int r = quarter * 32 + lane;                 // row in the query tile
+        const int rf = row0 + x * FA_BM + r;
+        if (x == 0 || two) {
+            const bool row_valid = rf < rows_total;
+            const int pos_r = row_valid ? start + rf / G : -1;
+            const int lo_r = row_valid ? fa_window_lo(pos_r, p.window) : 0;
+            const unsigned lane_base = (unsigned)(quarter * 32) << 16;
+            const unsigned tmem_s = tmem_base + S_COL + x * 128 + lane_base;
+            const unsigned tmem_o = tmem_base + O_COL + x * 128 + lane_base;
+            // the rows of this query tile: a key tile is taken without masks when all of them see all of it
+            const int xrow0 = row0 + x * FA_BM;
+            const bool rows_full = xrow0 + FA_BM <= rows_total;
+            const int xpos_first = start + xrow0 / G;
+            const int xlo_last = fa_window_lo(start + (min(xrow0 + FA_BM, rows_total) - 1) / G, p.window);
+            float m_run = -INFINITY, l_run = 0.0f;
+            bool alive = true;
+            for (int j = 0; j < num_tiles && alive; ++j) {
+                const int k0 = kbegin + j * FA_BN;
+                FA_T0();
+                if (!fa_mbar_wait(&s_full[x], j & 1, (5u << 24) | (x << 20) | j, failed)) { alive = false; break; }
+                if (warp == 2) FA_ACC(8);
+                fa_fence_after();
+                const bool full_tile = rows_full && k0 + FA_BN - 1 <= xpos_first && k0 >= xlo_last && k0 + FA_BN <= kend;
+                const float mx = (full_tile ? fa_row_max<false>(tmem_s, k0, pos_r, lo_r, kend)
+                                            : fa_row_max<true>(tmem_s, k0, pos_r, lo_r, kend)) * p.scale_log2;   // the scale is positive
+                // The reference point of the exponentials moves only when the maximum grew by more than 2^8:
+                // probabilities stay below 256, and the running output is rescaled rarely.
+                float alpha = 1.0f;
+                if (mx > m_run + 8.0f) { alpha = fa_ex2(m_run - mx); m_run = mx; }     // m_run = -inf gives alpha 0
+                const float base = (m_run == -INFINITY) ? 0.0f : m_run;
+                if (warp == 2) FA_ACC(9);
+                // the previous P V of this query tile must be complete before O is rescaled and P is overwritten
+                if (j > 0 && !fa_mbar_wait(&pv_done[x], (j - 1) & 1, (6u << 24) | (x << 20) | j, failed)) { alive = false; break; }
+                if (warp == 2) FA_ACC(10);
+                fa_fence_after();
+                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        float o[32];
+                        fa_tmem_ld32(tmem_o + c, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                        fa_tmem_st32(tmem_o + c, o);
+                    }
+                }
+                if (warp == 2) FA_ACC(11);
+                const float lsum = full_tile ? fa_row_probs<false>(tmem_s, p.scale_log2, base, k0, pos_r, lo_r, kend)
+                                             : fa_row_probs<true>(tmem_s, p.scale_log2, base, k0, pos_r, lo_r, kend);
+                l_run = l_run * alpha + lsum;
+                fa_fence_before();
+                __syncwarp();
+                if (lane == 0) fa_mbar_arrive(&p_ready[x]);
+                if (warp == 2) FA_ACC(12);
+            }
+            // ---------------- output: O / l ----------------
+            if (alive && num_tiles > 0 && fa_mbar_wait(&pv_done[x], (num_tiles - 1) & 1, (7u << 24) | (x << 20), failed)) {
+                fa_fence_after();
+                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                bf16* orow = p.out + (size_t)(tok_off + (row_valid ? rf / G : 0)) * p.nq * D + (size_t)(kvh * G + (row_valid ? rf % G : 0)) * D;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    float o[32];
+                    fa_tmem_ld32(tmem_o + c, o);
+                    if (row_valid) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 w;
+                            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[q4 * 8 + 0] * inv, o[q4 * 8 + 1] * inv);
+                            __nv_bfloat162 t1 = __floats2bfloat162_rn(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv);
+                            __nv_bfloat162 t3 = __floats2bfloat162_rn(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
+                            w.x = *reinterpret_cast<unsigned*>(&t0); w.y = *reinterpret_cast<unsigned*>(&t1);
+                            w.z = *reinterpret_cast<unsigned*>(&t2); w.w = *reinterpret_cast<unsigned*>(&t3);
+                            *reinterpret_cast<uint4*>(orow + c + q4 * 8) = w;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---------------- common exit ----------------
+    fa_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        fa_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 fa_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+    return fn;
+}
+
+// the page pool as a [rows, D] bf16 matrix; boxes of page_size rows x 64 columns, 128-byte swizzle
+static int fa_make_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
+    PFN_cuTensorMapEncodeTiled_v12000 encode = fa_encode_fn();
+    if (encode == nullptr) return pi_refuse("pi_attention_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)PI_HEAD_DIM, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)PI_HEAD_DIM * sizeof(bf16)};
+    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return pi_refuse("pi_attention_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+PI_EXPORT int pi_attention_tcgen05_status(unsigned* status) {
+    unsigned zero = 0;
+    cudaError_t err = cudaMemcpyFromSymbol(status, g_fa_status, sizeof(unsigned));
+    if (err == cudaSuccess) err = cudaMemcpyToSymbol(g_fa_status, &zero, sizeof(unsigned));
+    if (err != cudaSuccess) {
+        snprintf(g_pi_error, sizeof(g_pi_error), "pi_attention_tcgen05_status: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
+    return 0;
+}
+
+#ifdef FA_PROFILE
+PI_EXPORT int pi_attention_tcgen05_profile(unsigned long long* out16) {
+    unsigned long long zero[16] = {0};
+    cudaMemcpyFromSymbol(out16, g_fa_prof, sizeof(zero));
+    cudaMemcpyToSymbol(g_fa_prof, zero, sizeof(zero));
+    return 0;
+}
+#endif
+
+PI_EXPORT int pi_attention_tcgen05_supported(int page_size) {
+    return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+}
+
+// Prompt portions only: segments of one token are skipped (run the decode kernel for those).
+PI_EXPORT int pi_attention_tcgen05(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
+                                   const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                                   const int* seg_start, const int* seg_len, void* out, int num_segments, int max_seg_len,
+                                   int nq, int nkv, int page_size, int window, float scale, cudaStream_t stream) {
+    if (num_segments <= 0 || max_seg_len <= 0) return 0;
+    if (!(scale > 0.0f)) return pi_refuse("pi_attention_tcgen05: the score scale must be positive");
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return pi_refuse("pi_attention_tcgen05: nq=%d must be a positive multiple of nkv=%d", nq, nkv);
+    if (!pi_attention_tcgen05_supported(page_size)) return pi_refuse("pi_attention_tcgen05: page size %d is not one of 8, 16, 32, 64, 128", page_size);
+    if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)kcache & 127) || ((uintptr_t)vcache & 127))
+        return pi_refuse("pi_attention_tcgen05: q must be 16-byte aligned with a stride that is a multiple of 8, pages 128-byte aligned");
+    CUtensorMap mk, mv;
+    const long long rows = num_pages * nkv * page_size;
+    int rc = fa_make_map(&mk, kcache, rows, page_size);
+    if (rc) return rc;
+    rc = fa_make_map(&mv, vcache, rows, page_size);
+    if (rc) return rc;
+    FaParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.bt_stride = bt_stride;
+    p.seg_off = seg_off; p.seg_slot = seg_slot; p.seg_start = seg_start; p.seg_len = seg_len;
+    p.out = (bf16*)out; p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.page_size = page_size; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.tiles_per_seg = (int)(((long long)max_seg_len * p.group + FA_ROWS - 1) / FA_ROWS);
+    p.num_segments = num_segments;
+    const long long ctas = (long long)num_segments * p.tiles_per_seg * nkv;
+    if (ctas > 2147483647LL) return pi_refuse("pi_attention_tcgen05: %lld tiles are beyond the grid limit", ctas);
+    static bool configured = false;
+    constexpr unsigned tile_bytes = (PI_HEAD_DIM / 64) * 128 * 128;
+    const size_t smem = (size_t)(2 + FA_STAGES) * tile_bytes + (2 * FA_STAGES + 6) * 8 + 16 + 1024;
+    auto kernel = attn_tcgen05_kernel<PI_HEAD_DIM>;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) {
+            snprintf(g_pi_error, sizeof(g_pi_error), "pi_attention_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+            return (int)err;
+        }
+        configured = true;
+    }
+    pi_launch(kernel, dim3((unsigned)ctas), dim3(FA_THREADS), smem, stream, mk, mv, p);
+    return pi_check_launch("pi_attention_tcgen05");
+}
+
+#else   // head sizes this kernel does not take
+
+PI_EXPORT int pi_attention_tcgen05_supported(int page_size) { (void)page_size; return 0; }
+
+#endif

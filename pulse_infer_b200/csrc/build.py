@@ -32,6 +32,7 @@ SOURCES = {
     "sampling": "sampling.cu",
 }
 ATTENTION_MMA_SOURCE = "attention_mma.cu"
+ATTENTION_TCGEN05_SOURCE = "attention_tcgen05.cu"
 HEADERS = ["common.cuh", "attention_noalloc.h"]
 
 _lock = threading.Lock()
@@ -116,6 +117,11 @@ def library_path(name: str, head_dim: int | None = None) -> str:
                              f"in 16..256, got {head_dim}")
         source, defines, label = ATTENTION_MMA_SOURCE, [f"-DPI_HEAD_DIM={head_dim}"], f"attention (head size {head_dim})"
         stem = f"attention_mma_d{head_dim}"
+    elif name == "attention_tcgen05":
+        if head_dim not in (64, 128):
+            raise BuildError(f"the tcgen05 attention kernel takes head sizes 64 and 128, got {head_dim}")
+        source, defines, label = ATTENTION_TCGEN05_SOURCE, [f"-DPI_HEAD_DIM={head_dim}"], f"tcgen05 attention (head size {head_dim})"
+        stem = f"attention_tcgen05_d{head_dim}"
     elif name in SOURCES:
         source, defines, label, stem = SOURCES[name], [], name, name
     else:
@@ -132,4 +138,5 @@ def build_all(head_dims=(16, 32, 48, 64, 128)) -> list[str]:
     """Compile every library (attention for the given head sizes); used by the build check."""
     paths = [library_path(name) for name in SOURCES]
     paths += [library_path("attention_mma", d) for d in head_dims]
+    paths += [library_path("attention_tcgen05", d) for d in head_dims if d in (64, 128)]
     return paths

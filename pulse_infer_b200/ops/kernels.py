@@ -262,11 +262,44 @@ def attention_num_splits(pos: int, window: int | None, split_keys: int = SPLIT_K
     return (pos + 1 - lo_al + split_keys - 1) // split_keys
 
 
+TCGEN05_ATTENTION = os.environ.get("PULSE_TCGEN05_ATTENTION", "1") != "0"
+
+
+def attention_tcgen05_usable(head_dim: int, page_size: int) -> bool:
+    return TCGEN05_ATTENTION and head_dim in (64, 128) and page_size in (8, 16, 32, 64, 128)
+
+
+def attention_tcgen05(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len,
+                      num_tokens: int, num_segments: int, max_seg_len: int, nq: int, nkv: int, head_dim: int,
+                      page_size: int, window: int | None, scale: float, out: torch.Tensor) -> torch.Tensor:
+    """Prompt portions (segments of more than one token) on tcgen05 tensor cores; rows of single-token
+    segments in ``out`` are left untouched (see csrc/attention_tcgen05.cu)."""
+    _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, out)
+    _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 attention kernel takes bfloat16 only")
+    lib = _lib("attention_tcgen05", head_dim)
+    _check(lib, lib.pi_attention_tcgen05(
+        _p(q), c_int(q_stride), _p(kcache), _p(vcache), ctypes.c_longlong(kcache.shape[0]), _p(block_table),
+        c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), c_int(num_segments),
+        c_int(max_seg_len), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale), _stream()),
+        "attention_tcgen05")
+    return out
+
+
+def attention_tcgen05_status(head_dim: int) -> int:
+    lib = _lib("attention_tcgen05", head_dim)
+    status = ctypes.c_uint(0)
+    _check(lib, lib.pi_attention_tcgen05_status(ctypes.byref(status)), "attention_tcgen05_status", launches=0)
+    return int(status.value)
+
+
 def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len,
                   token_seg, num_tokens: int, num_segments: int, max_seg_len: int, has_prompt: bool, has_decode: bool,
                   max_splits: int, part_acc, part_ml, nq: int, nkv: int, head_dim: int, page_size: int,
                   window: int | None, scale: float, out: torch.Tensor | None = None,
-                  split_keys: int = SPLIT_KEYS, prefetch: torch.Tensor | None = None) -> torch.Tensor:
+                  split_keys: int = SPLIT_KEYS, prefetch: torch.Tensor | None = None,
+                  prompt_on_tcgen05: bool = True) -> torch.Tensor:
     """Tensor-core paged attention for bfloat16 over request segments (see csrc/attention_mma.cu)."""
     _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml)
     _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
@@ -274,6 +307,13 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
         raise KernelError("the tensor-core attention kernel takes bfloat16 only")
     if out is None:
         out = torch.empty((num_tokens, nq * head_dim), dtype=q.dtype, device=q.device)
+    if has_prompt and prompt_on_tcgen05 and attention_tcgen05_usable(head_dim, page_size):
+        # prompt portions on the tcgen05 kernel, single tokens (if any) on the decode kernel below
+        attention_tcgen05(q, q_stride, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, num_tokens,
+                          num_segments, max_seg_len, nq, nkv, head_dim, page_size, window, scale, out)
+        if not has_decode:
+            return out
+        has_prompt = False
     if has_decode and max_splits > 1:
         need = num_tokens * nq * max_splits
         if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:

@@ -166,7 +166,11 @@ def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengt
         out = ops.attention_mma(qflat, nq * d, kv.kcache, kv.vcache, kv.table_dev, meta["seg_off"], meta["seg_slot"],
                                 meta["seg_start"], meta["seg_len"], meta["token_seg"], T, len(segs), max(lens),
                                 any(n > 1 for n in lens), any(n == 1 for n in lens), splits, acc, ml, nq, nkv, d, page,
-                                window, scale)
+                                window, scale, prompt_on_tcgen05=(impl == "tcgen05"))
+        if impl == "tcgen05":
+            if not ops.attention_tcgen05_usable(d, page):
+                pytest.skip("the tcgen05 kernel takes head sizes 64 / 128 and page sizes 8..128")
+            assert ops.attention_tcgen05_status(d) == 0
     out = out.cpu().double().reshape(T, nq, d)
     worst = 0.0
     for (slot, start, n), off in zip(segs, meta["seg_off"].tolist()):
@@ -177,7 +181,7 @@ def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengt
 
 
 ATTN_SHAPES = [  # nq, nkv, d, page
-    (4, 2, 16, 8), (8, 1, 32, 16), (6, 2, 48, 16), (3, 3, 64, 4), (32, 8, 128, 16), (5, 1, 80, 8), (2, 1, 256, 16),
+    (8, 2, 128, 16), (6, 3, 64, 8), (4, 2, 16, 8), (8, 1, 32, 16), (6, 2, 48, 16), (3, 3, 64, 4), (32, 8, 128, 16), (5, 1, 80, 8), (2, 1, 256, 16),
     (40, 2, 64, 16), (12, 1, 64, 16), (16, 1, 32, 8), (7, 7, 96, 16)]
 
 
@@ -193,9 +197,11 @@ def test_attention_simple_float32(nq, nkv, d, page, window):
 
 @pytest.mark.parametrize("nq,nkv,d,page", [s for s in ATTN_SHAPES if s[2] % 16 == 0])
 @pytest.mark.parametrize("window", [None, 37])
-@pytest.mark.parametrize("impl", ["mma", "simple"])
+@pytest.mark.parametrize("impl", ["mma", "simple", "tcgen05"])
 def test_attention_bfloat16_prompt_and_decode(nq, nkv, d, page, window, impl):
     dev, ops = need_gpu(), _ops()
+    if impl == "tcgen05" and not ops.attention_tcgen05_usable(d, page):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 / 128 and page sizes 8..128")
     lengths = [150, 70, 301, 9, 1000]
     # portions at odd offsets, single tokens at page edges (63|64, 255|256), one long decode that is split
     segs = [(0, 100, 50), (1, 69, 1), (2, 0, 301), (3, 7, 2), (4, 999, 1)]
@@ -210,7 +216,8 @@ def test_attention_mma_decode_every_edge(ctx):
     assert err < 0.03
 
 
-@pytest.mark.parametrize("impl,dtype", [("mma", torch.bfloat16), ("simple", torch.bfloat16), ("simple", torch.float32)])
+@pytest.mark.parametrize("impl,dtype", [("mma", torch.bfloat16), ("tcgen05", torch.bfloat16), ("simple", torch.bfloat16),
+                                        ("simple", torch.float32)])
 @pytest.mark.parametrize("key_pos", [0, 15, 16, 300, 511, 512, 700])
 def test_attention_finds_one_far_key(impl, dtype, key_pos):
     """One key among hundreds carries nearly all the weight: the output must be that key's value."""
@@ -226,10 +233,22 @@ def test_attention_finds_one_far_key(impl, dtype, key_pos):
 def test_attention_window_edge_exact():
     """Keys just outside the window hold huge values; any leak shows."""
     dev, ops = need_gpu(), _ops()
-    for impl, dtype in (("mma", torch.bfloat16), ("simple", torch.float32)):
+    for impl, dtype in (("mma", torch.bfloat16), ("tcgen05", torch.bfloat16), ("simple", torch.float32)):
         for window in (1, 16, 17, 64, 65):
-            err = _attention_case(ops, dev, dtype, impl, 4, 2, 32, 16, window, [(0, 190, 10), (1, 99, 1)], [200, 100])
+            err = _attention_case(ops, dev, dtype, impl, 4, 2, 64, 16, window, [(0, 190, 10), (1, 99, 1)], [200, 100])
             assert err < (0.03 if dtype == torch.bfloat16 else 2e-5)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 8), (10, 2, 128, 64), (4, 1, 64, 128), (3, 1, 128, 32)])
+@pytest.mark.parametrize("window", [None, 1, 130, 300])
+def test_attention_tcgen05_long_portions(nq, nkv, d, page, window):
+    """Portions of several 128-row tiles over several 128-key tiles, starting inside a page and inside a tile;
+    windows that end inside a tile and span more than one; a single token beside them goes to the decode kernel."""
+    dev, ops = need_gpu(), _ops()
+    lengths = [700, 131, 1029, 40]
+    segs = [(0, 100, 600), (1, 0, 131), (2, 517, 512), (3, 39, 1)]
+    err = _attention_case(ops, dev, torch.bfloat16, "tcgen05", nq, nkv, d, page, window, segs, lengths, seed=nq + page)
+    assert err < 0.03
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 515, 96), (33, 515, 100), (64, 64, 16), (130, 77, 1000), (7, 4096, 4096)])
