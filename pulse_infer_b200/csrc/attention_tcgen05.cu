@@ -1,19 +1,24 @@
 // Paged flash attention for prompt portions on the 5th-generation tensor cores (bfloat16).
 //
-// A CTA owns 128 query rows - (token, head-in-group) pairs of one kv head of one request segment, as in
-// attention_mma.cu - and walks the visible keys in tiles of 128:
-//   S = Q K^T      tcgen05.mma, M 128 x N 128, both operands K-major from 128-byte-swizzled shared memory,
-//                  accumulator in TMEM; two S buffers so the next tile's scores are computed while the
-//                  current tile is in the softmax
-//   softmax        four warps, ONE THREAD PER ROW: the row's 128 scores come out of TMEM with tcgen05.ld, so
-//                  max / exp2 / sum need no shuffles; probabilities go to shared memory as bf16 in the
-//                  swizzled K-major layout; the running output in TMEM is rescaled in place (tcgen05.ld/st)
-//                  only when a row's maximum moved
-//   O += P V       tcgen05.mma, A = P from shared memory, B = V tile used MN-major (rows of V are keys)
-// Keys and values arrive by TMA, one box per (page, 64-wide half of the head): cp.async.bulk.tensor.2d over
-// the page pool seen as a [pages * kv heads * page size, head size] matrix; the page ids come from the block
-// table.  Roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5 softmax / output.
-// Every mbarrier wait is bounded; on a timeout the kernel records a code, all roles fall through, TMEM is freed.
+// A CTA owns 256 query rows - (token, head-in-group) pairs of one kv head of one request segment, as in
+// attention_mma.cu - as two query tiles of 128, and walks the visible keys in tiles of 128:
+//   S_x = Q_x K^T   tcgen05.mma, M 128 x N 128, both operands K-major from 128-byte-swizzled shared memory,
+//                   accumulator in tensor memory (128 columns per query tile)
+//   softmax         four warps per query tile, ONE THREAD PER ROW: the row's scores come out of tensor memory
+//                   with tcgen05.ld, so max / exp2 / sum need no shuffles.  The probabilities go back into
+//                   tensor memory as bf16 pairs over the scores already read (tcgen05.st).  The reference
+//                   point of the exponentials moves only when the maximum grew by more than 2^8, so the
+//                   running output is rescaled (tcgen05.ld / st) rarely.
+//   O_x += P_x V    tcgen05.mma with the A operand from tensor memory and V from shared memory, MN-major
+//                   (rows of V are keys)
+// While one query tile is in its softmax the tensor pipe works for the other.  Tensor memory: S_0, S_1, O_0,
+// O_1 of 128 columns each - all 512.  Keys and values arrive by TMA through a ring of tiles (K(0) V(0) K(1)
+// ...), one box per (page, 64-wide half of the head): cp.async.bulk.tensor.2d over the page pool seen as a
+// [pages * kv heads * page size, head size] matrix; the lanes of the producer warp look the page ids up in
+// the block table together.  Roles: warp 0 TMA producer, warp 1 MMA issuer + owner of tensor memory, warps
+// 2-5 softmax / output of query tile 0, warps 6-9 of query tile 1.
+// Every mbarrier wait is bounded; on a timeout the kernel records a code, all roles fall through and tensor
+// memory is freed.
 //
 // Needs: head size 64 or 128 (PI_HEAD_DIM), page size in {8, 16, 32, 64, 128}.  Segments of one token are
 // left to the decode kernel.

@@ -103,3 +103,6 @@ class ModelRunner:
             status = ops.gemm_tcgen05_status()
             if status:
                 raise StepError(f"a wait inside the tcgen05 product ran out (status {status:#x})")
+            status = ops.attention_tcgen05_loaded_status()
+            if status:
+                raise StepError(f"a wait inside the tcgen05 attention kernel ran out (status {status:#x})")

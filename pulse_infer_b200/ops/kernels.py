@@ -102,6 +102,8 @@ def preload(head_dims=(), simple_attention: bool = False, float32_products: bool
         _lib("attention_simple")
     for d in head_dims:
         _lib("attention_mma", d)
+        if not float32_products and d in (64, 128) and os.environ.get("PULSE_TCGEN05_ATTENTION", "1") != "0":
+            _lib("attention_tcgen05", d)
 
 
 # ---- embedding --------------------------------------------------------------------------------------
@@ -285,6 +287,16 @@ def attention_tcgen05(q: torch.Tensor, q_stride: int, kcache, vcache, block_tabl
         c_int(max_seg_len), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale), _stream()),
         "attention_tcgen05")
     return out
+
+
+def attention_tcgen05_loaded_status() -> int:
+    """The first non-zero status among the tcgen05 attention libraries that this process has loaded."""
+    for (name, head_dim) in list(_LIBS):
+        if name == "attention_tcgen05":
+            status = attention_tcgen05_status(head_dim)
+            if status:
+                return status
+    return 0
 
 
 def attention_tcgen05_status(head_dim: int) -> int:

@@ -51,7 +51,7 @@ def _plain(plain_cache, folder, tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_then_last_32_one_by_one_then_portions(name, dtype, model_folders, plain_cache):
     from pulse_infer_b200.engine import Segment
     need_gpu()
@@ -91,7 +91,28 @@ def test_whole_then_last_32_one_by_one_then_portions(name, dtype, model_folders,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_long_prompt_in_large_portions(dtype, model_folders, plain_cache):
+    """Portions of several hundred tokens: several query tiles over several key tiles, a window that ends inside
+    a key tile (head size 64: the tcgen05 attention kernel in bfloat16), then single tokens."""
+    from pulse_infer_b200.engine import Segment
+    need_gpu()
+    folder, cfg = model_folders["D"], CONFIGS["D"]
+    toks = random_tokens(77, 600, cfg.vocab_size)
+    want = _plain(plain_cache, folder, toks)
+    runner = _runner(folder, dtype, num_pages=48, max_tokens_per_request=768)
+    runner.open("r")
+    at = 0
+    for c in (257, 130, 200, 1, 1, 9, 1, 1):
+        got = runner.step([Segment("r", toks[at:at + c], list(range(c)))])
+        _check(got, want[at:at + c], dtype, f"portion [{at}, {at + c})")
+        at += c
+    runner.check_device_errors()
+    runner.close("r")
+    runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_with_reused_pages(name, dtype, model_folders, plain_cache):
     """Up to four live requests, portions of some beside decoded tokens of others, in a pool so small
     that pages of finished requests are handed to the next ones at once."""

@@ -1,7 +1,8 @@
 """The tiny configurations the tests run on.  They differ in every size and option: layer count,
 widths, grouped vs multi-query heads, q width equal / unequal to the hidden size, head size, theta,
 eps, tying, an odd vocabulary, the window.  A and B are the ones the golden outputs of the reference's
-CPU model exist for; C adds windowed layers mixed with full ones, which the reference does not have."""
+CPU model exist for; C adds windowed layers mixed with full ones, which the reference does not have; D has
+the head size (64) that puts prompt portions on the tcgen05 attention kernel in bfloat16."""
 from pulse_infer_b200.config import Qwen3Config
 
 TINY_A = Qwen3Config(
@@ -20,5 +21,11 @@ TINY_C = Qwen3Config(
     rms_norm_eps=3e-6, rope_theta=50000.0, tie_word_embeddings=False, torch_dtype="bfloat16", eos_token_ids=(7,),
     layer_types=("full_attention", "sliding_attention", "sliding_attention", "full_attention"), sliding_window=24)
 
-SEEDS = {"A": 0, "B": 1, "C": 2}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+TINY_D = Qwen3Config(
+    architecture="Qwen3ForCausalLM", hidden_size=112, intermediate_size=208, num_hidden_layers=2,
+    num_attention_heads=6, num_key_value_heads=3, head_dim=64, vocab_size=333, max_position_embeddings=1024,
+    rms_norm_eps=2e-6, rope_theta=20000.0, tie_word_embeddings=True, torch_dtype="bfloat16", eos_token_ids=(3,),
+    layer_types=("sliding_attention", "full_attention"), sliding_window=150)
+
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
