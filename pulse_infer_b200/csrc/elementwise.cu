@@ -344,12 +344,71 @@ __global__ void qk_norm_rope_write_kernel(TA* __restrict__ qkv, int row_stride, 
         dst = base + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * d;
     }
 
+    // 16-bit activations whose rows and heads start on 8-byte boundaries move in 8-byte pieces
+    const bool wide = sizeof(TA) == 2 && (d & 3) == 0 && (row_stride & 3) == 0 && ((uintptr_t)qkv & 7) == 0 &&
+                      ((uintptr_t)kcache & 7) == 0 && ((uintptr_t)vcache & 7) == 0;
     if (head >= nq + nkv) {  // value head: plain copy
-        for (int e = lane; e < d; e += 32) dst[e] = src[e];
+        if (wide) {
+            for (int e = lane; e < d / 4; e += 32) reinterpret_cast<uint2*>(dst)[e] = reinterpret_cast<const uint2*>(src)[e];
+        } else {
+            for (int e = lane; e < d; e += 32) dst[e] = src[e];
+        }
         return;
     }
 
     const TW* w = head < nq ? qw : kw;
+    if (sizeof(TA) == 2 && wide && adjacent) {
+        // a lane takes two adjacent pairs (four elements) at a time: the same arithmetic as below, wider accesses
+        const bf16* s16 = reinterpret_cast<const bf16*>(src);
+        bf16* d16 = reinterpret_cast<bf16*>(dst);
+        constexpr int QUADS = QK_MAX_PAIRS / 2;
+        float x[QUADS][4];
+        float ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < QUADS; ++k) {
+            const int qd = lane + 32 * k;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[k][i] = 0.0f;
+            if (qd < d / 4) {
+                const uint2 raw = reinterpret_cast<const uint2*>(s16)[qd];
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                x[k][0] = __low2float(a); x[k][1] = __high2float(a); x[k][2] = __low2float(b); x[k][3] = __high2float(b);
+                ss += x[k][0] * x[k][0] + x[k][1] * x[k][1];
+                ss += x[k][2] * x[k][2] + x[k][3] * x[k][3];
+            }
+        }
+        float inv = 1.0f;
+        if (has_norm) {
+            ss = warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)d + eps);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < QUADS; ++k) {
+            const int qd = lane + 32 * k;
+            if (qd < d / 4) {
+                float v[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = has_norm ? x[k][i] * inv * to_float<TW>(w[4 * qd + i]) : x[k][i];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int p = 2 * qd + h;
+                    if (p < rot_pairs) {
+                        const float c = cos_t[(size_t)t * rot_pairs + p], sn = sin_t[(size_t)t * rot_pairs + p];
+                        const float r0 = v[2 * h] * c - v[2 * h + 1] * sn;
+                        const float r1 = v[2 * h] * sn + v[2 * h + 1] * c;
+                        v[2 * h] = r0; v[2 * h + 1] = r1;
+                    }
+                }
+                const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+                uint2 raw;
+                raw.x = *reinterpret_cast<const unsigned*>(&a); raw.y = *reinterpret_cast<const unsigned*>(&b);
+                reinterpret_cast<uint2*>(d16)[qd] = raw;
+            }
+        }
+        return;
+    }
     const int half_pairs = d / 2;
     float x0[QK_MAX_PAIRS], x1[QK_MAX_PAIRS];
     float ss = 0.0f;
