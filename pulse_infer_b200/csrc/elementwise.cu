@@ -197,8 +197,8 @@ PI_EXPORT int pi_add_rmsnorm(float* h, const void* delta, const void* weight, in
 
 // ---------------------------------------------------------------------------------------------------
 // SiLU(gate) * up on the fused [n, 2*inter] output of the gate_up product: out[n, inter].
-// blocked = 0: columns are [all gate | all up].  blocked = 1: columns come in blocks of 32, 16 gate features
-// followed by their 16 up features (the layout the tcgen05 product's gated epilogue wants of the weight rows).
+// blocked = 0: columns are [all gate | all up].  blocked = 1: columns come in blocks of 16, 8 gate features
+// followed by their 8 up features (the layout the products' gated epilogues want of the weight rows).
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total, int blocked,
@@ -210,8 +210,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     if (e >= total) return;
     const size_t row = e / inter;
     const int col = (int)(e % inter);
-    const int gcol = blocked ? (col / 16) * 32 + col % 16 : col;
-    const int ucol = blocked ? gcol + 16 : inter + col;
+    const int gcol = blocked ? (col / 8) * 16 + col % 8 : col;
+    const int ucol = blocked ? gcol + 8 : inter + col;
     const float g = to_float<T>(gu[row * 2 * (size_t)inter + gcol]);
     const float u = to_float<T>(gu[row * 2 * (size_t)inter + ucol]);
     out[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
@@ -230,8 +230,8 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
     const int vecs_per_row = inter / VEC;
     const size_t row = idx / vecs_per_row;
     const int col = (int)(idx % vecs_per_row) * VEC;
-    const int gcol = blocked ? (col / 16) * 32 + col % 16 : col;     // VEC divides 16: a vector stays inside a block
-    const int ucol = blocked ? gcol + 16 : inter + col;
+    const int gcol = blocked ? (col / 8) * 16 + col % 8 : col;       // VEC divides 8: a vector stays inside a block
+    const int ucol = blocked ? gcol + 8 : inter + col;
     const Pack g = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + gcol);
     const Pack u = *reinterpret_cast<const Pack*>(gu + row * 2 * (size_t)inter + ucol);
     Pack o;
@@ -247,7 +247,7 @@ PI_EXPORT int pi_silu_mul(const void* gate_up, void* out, int dtype, int n, int 
                           unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (inter <= 0) return pi_refuse("pi_silu_mul: inter=%d must be positive", inter);
-    if (blocked && inter % 16 != 0) return pi_refuse("pi_silu_mul: the blocked layout needs inter %% 16 == 0 (inter=%d)", inter);
+    if (blocked && inter % 8 != 0) return pi_refuse("pi_silu_mul: the blocked layout needs inter %% 8 == 0 (inter=%d)", inter);
     const size_t total = (size_t)n * inter;
     const int threads = 256;
     if (dtype == PI_BF16 && inter % 8 == 0) {

@@ -40,7 +40,9 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], unsigned a0, unsigned a
 }
 
 // MT: tiles of 8 rows of x; SM_WARPS: warps per CTA, each takes 1/SM_WARPS of K; DOUBLE: two register sets
-template <int MT, typename TO, int SM_WARPS, bool DOUBLE, int MIN_CTAS>
+// GATED: the 16 rows of W of a CTA are 8 gate features followed by their 8 up features, and the CTA writes
+// silu(gate) * up for its 8 features (out has N / 2 columns).
+template <int MT, typename TO, int SM_WARPS, bool DOUBLE, int MIN_CTAS, bool GATED>
 __global__ void __launch_bounds__(SM_WARPS * 32, MIN_CTAS)
 gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw, TO* __restrict__ out, int ldo,
                     int M, int N, int K) {
@@ -119,31 +121,44 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         partial[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < SM_FEATURES * MT * 8; idx += SM_WARPS * 32) {
-        const int m = idx / SM_FEATURES, f = idx % SM_FEATURES;   // neighbouring threads take neighbouring features
-        if (m >= M || n0 + f >= N) continue;
-        float sum = 0.0f;
+    if constexpr (GATED) {
+        for (int idx = threadIdx.x; idx < (SM_FEATURES / 2) * MT * 8; idx += SM_WARPS * 32) {
+            const int m = idx / (SM_FEATURES / 2), f = idx % (SM_FEATURES / 2);
+            if (m >= M || n0 + f + SM_FEATURES / 2 >= N) continue;
+            float gate = 0.0f, up = 0.0f;
 #pragma unroll
-        for (int w = 0; w < SM_WARPS; ++w) sum += partial[w][f][m];
-        out[(size_t)m * ldo + n0 + f] = from_float<TO>(sum);
+            for (int w = 0; w < SM_WARPS; ++w) { gate += partial[w][f][m]; up += partial[w][f + SM_FEATURES / 2][m]; }
+            out[(size_t)m * ldo + n0 / 2 + f] = from_float<TO>(gate / (1.0f + expf(-gate)) * up);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < SM_FEATURES * MT * 8; idx += SM_WARPS * 32) {
+            const int m = idx / SM_FEATURES, f = idx % SM_FEATURES;   // neighbouring threads take neighbouring features
+            if (m >= M || n0 + f >= N) continue;
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < SM_WARPS; ++w) sum += partial[w][f][m];
+            out[(size_t)m * ldo + n0 + f] = from_float<TO>(sum);
+        }
     }
 }
 
 template <int MT, int WARPS, bool DOUBLE, int MIN_CTAS>
 static void launch_small_m_shape(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M,
-                                 int N, int K, cudaStream_t stream) {
+                                 int N, int K, int gated, cudaStream_t stream) {
     const dim3 grid((unsigned)((N + SM_FEATURES - 1) / SM_FEATURES));
-    if (out_dtype == PI_F32)
-        pi_launch(gemm_small_m_kernel<MT, float, WARPS, DOUBLE, MIN_CTAS>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (float*)out, ldo, M, N, K);
+    if (gated)     // bf16 output only (checked by the caller)
+        pi_launch(gemm_small_m_kernel<MT, bf16, WARPS, DOUBLE, MIN_CTAS, true>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K);
+    else if (out_dtype == PI_F32)
+        pi_launch(gemm_small_m_kernel<MT, float, WARPS, DOUBLE, MIN_CTAS, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (float*)out, ldo, M, N, K);
     else
-        pi_launch(gemm_small_m_kernel<MT, bf16, WARPS, DOUBLE, MIN_CTAS>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K);
+        pi_launch(gemm_small_m_kernel<MT, bf16, WARPS, DOUBLE, MIN_CTAS, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)out, ldo, M, N, K);
 }
 
 // variant 0: chosen from the shape.  1: 8 warps, two register sets, 2 CTAs/SM.  2: 8 warps, two sets, 3 CTAs/SM.
 // 3: 16 warps, one set, 2 CTAs/SM (M <= 8 only).  4: 8 warps, one set, 4 CTAs/SM.
 template <int MT>
 static void launch_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                           int K, int variant, cudaStream_t stream) {
+                           int K, int variant, int gated, cudaStream_t stream) {
     const int tiles = (N + SM_FEATURES - 1) / SM_FEATURES;
     if (variant == 0) {   // from measurements on B200 at the sizes of 8B- to 32B-class models
         if (MT == 1) {
@@ -156,37 +171,45 @@ static void launch_small_m(const void* x, int ldx, const void* W, int ldw, void*
     }
     if (variant == 3 && MT != 1) variant = 1;
     switch (variant) {
-        case 2: launch_small_m_shape<MT, 8, true, 3>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
-        case 3: launch_small_m_shape<1, 16, false, 2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
-        case 4: launch_small_m_shape<MT, 8, false, 4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
-        default: launch_small_m_shape<MT, 8, true, 2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, stream); break;
+        case 2: launch_small_m_shape<MT, 8, true, 3>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, gated, stream); break;
+        case 3: launch_small_m_shape<1, 16, false, 2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, gated, stream); break;
+        case 4: launch_small_m_shape<MT, 8, false, 4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, gated, stream); break;
+        default: launch_small_m_shape<MT, 8, true, 2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, gated, stream); break;
     }
 }
 
 PI_EXPORT int pi_gemm_small_m_max_rows() { return 32; }
 
 static int gemm_small_m_impl(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                             int K, int variant, cudaStream_t stream) {
+                             int K, int variant, int gated, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 32) return pi_refuse("pi_gemm_small_m: %d rows; this kernel takes at most 32", M);
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
         return pi_refuse("pi_gemm_small_m: K=%d and the leading dimensions (%d, %d) must be positive multiples of 8", K, ldx, ldw);
-    if (ldx < K || ldw < K || ldo < N) return pi_refuse("pi_gemm_small_m: leading dimensions (%d, %d, %d) too small", ldx, ldw, ldo);
+    if (ldx < K || ldw < K || ldo < (gated ? N / 2 : N)) return pi_refuse("pi_gemm_small_m: leading dimensions (%d, %d, %d) too small", ldx, ldw, ldo);
+    if (gated && (out_dtype != PI_BF16 || N % SM_FEATURES != 0))
+        return pi_refuse("pi_gemm_small_m: the gated epilogue needs bf16 output and N %% %d == 0 (N=%d)", SM_FEATURES, N);
     if (((uintptr_t)x | (uintptr_t)W) & 15) return pi_refuse("pi_gemm_small_m: operands must be 16-byte aligned");
     if (out_dtype != PI_F32 && out_dtype != PI_BF16) return pi_refuse("pi_gemm_small_m: unknown output dtype code %d", out_dtype);
-    if (M <= 8) launch_small_m<1>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
-    else if (M <= 16) launch_small_m<2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
-    else launch_small_m<4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
+    if (M <= 8) launch_small_m<1>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, gated, stream);
+    else if (M <= 16) launch_small_m<2>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, gated, stream);
+    else launch_small_m<4>(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, gated, stream);
     return pi_check_launch("pi_gemm_small_m");
 }
 
 PI_EXPORT int pi_gemm_small_m(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
                               int K, cudaStream_t stream) {
-    return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, 0, stream);
+    return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, 0, 0, stream);
+}
+
+// out[M, N / 2] = silu(x Wg^T) * (x Wu^T) with the rows of W in blocks of 16: 8 gate features, then their 8 up features
+PI_EXPORT int pi_gemm_small_m_gated(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K,
+                                    cudaStream_t stream) {
+    return gemm_small_m_impl(x, ldx, W, ldw, out, PI_BF16, ldo, M, N, K, 0, 1, stream);
 }
 
 // the same with the launch shape forced (for measurements)
 PI_EXPORT int pi_gemm_small_m_variant(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M,
                                       int N, int K, int variant, cudaStream_t stream) {
-    return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, stream);
+    return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, 0, stream);
 }

@@ -121,21 +121,21 @@ struct TcParams {
     int ldo;
     int M, N, K;
     int out_f32;     // 1: float32 output, 0: bfloat16
-    int gated;       // 1: W rows are interleaved (gate_i, up_i) pairs per 16 columns block; see the epilogue
+    int gated;       // 1: W rows come in blocks of 16, 8 gate features and their 8 up features; see the epilogue
     int tiles_m, tiles_n;
 };
 
 // One 32-column chunk of an accumulator row goes to memory: plain (bf16 or f32), or through the gated activation.
 __device__ __forceinline__ void tc_store_chunk(const TcParams& p, int row, int col0, const float (&v)[32]) {
     if (p.gated) {
-        // columns come in blocks of 32: 16 gate features followed by their 16 up features;
+        // columns come in blocks of 16: 8 gate features followed by their 8 up features;
         // out[row, col0 / 2 + j] = silu(gate_j) * up_j  (out has N / 2 columns)
         const int col = col0 / 2;
         bf16* dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + col;
         alignas(16) bf16 packed[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const float g = v[j], u = v[16 + j];
+            const float g = v[(j >> 3) * 16 + (j & 7)], u = v[(j >> 3) * 16 + 8 + (j & 7)];
             packed[j] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
         }
         if (col + 16 <= p.N / 2 && (p.ldo & 7) == 0) {
@@ -535,8 +535,8 @@ PI_EXPORT int pi_gemm_tcgen05_status(unsigned* status) {
     return 0;
 }
 
-// gated = 1: W holds gate and up rows interleaved in blocks of 16 (rows 32b .. 32b+15 gate features 16b .. 16b+15,
-// rows 32b+16 .. 32b+31 the matching up features); out is [M, N / 2] bf16 = silu(gate) * up.
+// gated = 1: W holds gate and up rows interleaved in blocks of 8 (rows 16b .. 16b+7 gate features 8b .. 8b+7,
+// rows 16b+8 .. 16b+15 the matching up features); out is [M, N / 2] bf16 = silu(gate) * up.
 // mode 0: CTA pairs when M > 128, single CTAs otherwise; 1: single CTAs; 2: CTA pairs
 PI_EXPORT int pi_gemm_tcgen05(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
                               int K, int gated, int max_ctas, int mode, cudaStream_t stream) {
@@ -545,7 +545,7 @@ PI_EXPORT int pi_gemm_tcgen05(const void* x, int ldx, const void* W, int ldw, vo
         return pi_refuse("pi_gemm_tcgen05: K=%d and the leading dimensions (%d, %d) must be positive multiples of 8", K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)W) & 15) return pi_refuse("pi_gemm_tcgen05: operands must be 16-byte aligned");
     if (out_dtype != PI_F32 && out_dtype != PI_BF16) return pi_refuse("pi_gemm_tcgen05: unknown output dtype code %d", out_dtype);
-    if (gated && (out_dtype != PI_BF16 || N % 32 != 0)) return pi_refuse("pi_gemm_tcgen05: the gated epilogue needs bf16 output and N %% 32 == 0 (N=%d)", N);
+    if (gated && (out_dtype != PI_BF16 || N % 16 != 0)) return pi_refuse("pi_gemm_tcgen05: the gated epilogue needs bf16 output and N %% 16 == 0 (N=%d)", N);
     const int BN = 256;
     const bool pairs_mode = mode == 2 || (mode == 0 && M > TC_BM);
     CUtensorMap mx, mw;

@@ -152,8 +152,8 @@ def add_rmsnorm(hidden: torch.Tensor, delta: torch.Tensor | None, weight: torch.
 # ---- SiLU(gate) * up ------------------------------------------------------------------------------------
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, prefetch: torch.Tensor | None = None,
              blocked: bool = False) -> torch.Tensor:
-    """gate_up [T, 2*I] -> [T, I].  Columns are [all gate | all up], or with ``blocked`` blocks of 32:
-    16 gate features followed by their 16 up features."""
+    """gate_up [T, 2*I] -> [T, I].  Columns are [all gate | all up], or with ``blocked`` blocks of 16:
+    8 gate features followed by their 8 up features."""
     _need_cuda(gate_up)
     _need_contig(gate_up=gate_up)
     T, two_i = gate_up.shape
@@ -364,8 +364,11 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = N
 SMALL_M_ROWS = 16         # up to this many rows the weight-streaming kernel is used instead of cuBLAS
 
 
-def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None = None) -> torch.Tensor:
-    """x bf16 [M <= 32, K], weight bf16 [N, K] -> [M, N] in bf16 or fp32: every weight read once."""
+def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None = None,
+                 gated: bool = False) -> torch.Tensor:
+    """x bf16 [M <= 32, K], weight bf16 [N, K] -> [M, N] in bf16 or fp32: every weight read once.
+    ``gated``: weight rows are gate/up features interleaved in blocks of 8 (see ``interleave_gate_up``) and the
+    result is silu(gate) * up, [M, N / 2] bf16."""
     _need_cuda(x, weight)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError("gemm_small_m takes bfloat16 operands")
@@ -375,9 +378,16 @@ def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, 
     N, K2 = weight.shape
     if K != K2:
         raise KernelError(f"inner sizes differ: {K} vs {K2}")
+    lib = _lib("gemm_small_m")
+    if gated:
+        if out is None:
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        _check(lib, lib.pi_gemm_small_m_gated(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
+                                              c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), _stream()),
+               "gemm_small_m_gated")
+        return out
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    lib = _lib("gemm_small_m")
     _check(lib, lib.pi_gemm_small_m(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
                                     c_int(_code(out_dtype)), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
                                     _stream()), "gemm_small_m")
@@ -387,7 +397,7 @@ def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, gated: bool = False,
                  out: torch.Tensor | None = None, max_ctas: int = 0, mode: int = 0) -> torch.Tensor:
     """x bf16 [M, K], weight bf16 [N, K] -> [M, N] on tcgen05 tensor cores (TMEM accumulators, TMA loads).
-    ``gated``: weight rows are gate/up features interleaved in blocks of 16 (see ``interleave_gate_up``) and the
+    ``gated``: weight rows are gate/up features interleaved in blocks of 8 (see ``interleave_gate_up``) and the
     result is silu(gate) * up, [M, N / 2] bf16.  ``mode``: 0 chosen from M, 1 single CTAs, 2 CTA pairs."""
     _need_cuda(x, weight)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
@@ -415,12 +425,18 @@ def gemm_tcgen05_status() -> int:
     return int(status.value)
 
 
+GATE_BLOCK = 8    # gate / up features per block of the interleaved layout
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-    """[I, K] gate and up weights -> [2I, K] with rows in blocks of 32: 16 gate rows, then their 16 up rows."""
+    """[I, K] gate and up weights -> [2I, K] with rows in blocks of 16: 8 gate rows, then their 8 up rows.
+    A 16-row tile of the small-M product and every 32-column chunk of the tcgen05 product's epilogue then
+    hold gate and up of the same features."""
     I, K = gate.shape
-    if I % 16:
-        raise KernelError("the interleaved layout needs an intermediate size that is a multiple of 16")
-    return torch.stack([gate.view(I // 16, 16, K), up.view(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()
+    B = GATE_BLOCK
+    if I % B:
+        raise KernelError(f"the interleaved layout needs an intermediate size that is a multiple of {B}")
+    return torch.stack([gate.view(I // B, B, K), up.view(I // B, B, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
