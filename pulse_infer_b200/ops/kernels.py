@@ -361,14 +361,40 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = N
     return out
 
 
+FUSE_NORMS = os.environ.get("PULSE_FUSE_NORMS", "1") != "0"   # decoding: norms prepared / finished inside the products
 SMALL_M_ROWS = 16         # up to this many rows the weight-streaming kernel is used instead of cuBLAS
 
 
+class NormedRows:
+    """The input of an RMSNorm over a few rows of the 32-bit residual, prepared by the product that last added to
+    the residual (``linear(..., residual=h, next_norm=...)``): ``scaled`` = bf16(h * norm weight) and ``partials``
+    [32, slots] = sums of h^2 per row and 16-feature tile.  The weight-streaming product takes both and scales
+    its outputs by rsqrt(mean(h^2) + eps), so the norm needs no kernel of its own; ``materialize()`` runs the norm
+    kernel for everyone else.  ``owner`` says whose norm this is (any object, compared by identity)."""
+
+    def __init__(self, hidden: torch.Tensor, weight: torch.Tensor, eps: float, act_dtype: torch.dtype,
+                 scaled: torch.Tensor, partials: torch.Tensor, owner=None):
+        self.hidden, self.weight, self.eps, self.act_dtype = hidden, weight, float(eps), act_dtype
+        self.scaled, self.partials, self.owner = scaled, partials, owner
+        self.shape, self.dtype = hidden.shape, act_dtype
+        self._value: torch.Tensor | None = None
+
+    def materialize(self) -> torch.Tensor:
+        if self._value is None:
+            self._value = add_rmsnorm(self.hidden, None, self.weight, self.eps, self.act_dtype)
+        return self._value
+
+
 def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None = None,
-                 gated: bool = False) -> torch.Tensor:
+                 gated: bool = False, residual: torch.Tensor | None = None, row_ssq: tuple | None = None,
+                 emit_norm: torch.Tensor | None = None):
     """x bf16 [M <= 32, K], weight bf16 [N, K] -> [M, N] in bf16 or fp32: every weight read once.
     ``gated``: weight rows are gate/up features interleaved in blocks of 8 (see ``interleave_gate_up``) and the
-    result is silu(gate) * up, [M, N / 2] bf16."""
+    result is silu(gate) * up, [M, N / 2] bf16.
+    ``residual`` (float32 [M, N]): the result is added to it in place and it is returned.  With ``emit_norm``
+    (the weight [N] of the RMSNorm that follows) the kernel also writes bf16(residual * emit_norm) and the
+    per-tile sums of residual^2, and (residual, scaled, partials) is returned.
+    ``row_ssq`` = (partials, eps): x is such a ``scaled`` tensor; outputs are scaled by rsqrt(mean + eps) per row."""
     _need_cuda(x, weight)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError("gemm_small_m takes bfloat16 operands")
@@ -379,18 +405,46 @@ def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, 
     if K != K2:
         raise KernelError(f"inner sizes differ: {K} vs {K2}")
     lib = _lib("gemm_small_m")
-    if gated:
+    if not gated and residual is None and row_ssq is None:
         if out is None:
-            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
-        _check(lib, lib.pi_gemm_small_m_gated(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
-                                              c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), _stream()),
-               "gemm_small_m_gated")
+            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        _check(lib, lib.pi_gemm_small_m(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
+                                        c_int(_code(out_dtype)), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
+                                        _stream()), "gemm_small_m")
         return out
-    if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    _check(lib, lib.pi_gemm_small_m(_p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out),
-                                    c_int(_code(out_dtype)), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
-                                    _stream()), "gemm_small_m")
+    scaled = partials = None
+    if residual is not None:
+        if gated or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N) or residual.stride(-1) != 1:
+            raise KernelError("gemm_small_m: the residual is float32 [M, N] and goes with a plain product")
+        _need_cuda(residual)
+        out, epilogue = residual, 2
+        if emit_norm is not None:
+            _need_cuda(emit_norm)
+            if emit_norm.numel() != N or not emit_norm.is_contiguous():
+                raise KernelError("gemm_small_m: the next norm's weight must hold N contiguous values")
+            scaled = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+            partials = torch.empty((32, lib.pi_gemm_small_m_tiles(c_int(N))), dtype=torch.float32, device=x.device)
+    else:
+        if emit_norm is not None:
+            raise KernelError("gemm_small_m: preparing the next norm goes with the residual epilogue")
+        epilogue = 1 if gated else 0
+        if gated:
+            out_dtype = torch.bfloat16
+        if out is None:
+            out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    ssq, eps = row_ssq if row_ssq is not None else (None, 0.0)
+    if ssq is not None:
+        _need_cuda(ssq)
+        if ssq.dtype != torch.float32 or ssq.dim() != 2 or ssq.shape[0] != 32 or not ssq.is_contiguous():
+            raise KernelError("gemm_small_m: the partial sums are float32 [32, slots]")
+    _check(lib, lib.pi_gemm_small_m_fused(
+        _p(x), c_int(x.stride(0)), _p(weight), c_int(weight.stride(0)), _p(out), c_int(_code(out.dtype)),
+        c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(epilogue), _p(ssq),
+        c_int(ssq.shape[1] if ssq is not None else 0), c_float(eps), _p(emit_norm),
+        c_int(_code(emit_norm.dtype) if emit_norm is not None else BF16), _p(scaled),
+        c_int(scaled.stride(0) if scaled is not None else 0), _p(partials), _stream()), "gemm_small_m_fused")
+    if scaled is not None:
+        return out, scaled, partials
     return out
 
 
@@ -439,10 +493,27 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(I // B, B, K), up.view(I // B, B, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def small_m_usable(rows: int, K: int, weight: torch.Tensor) -> bool:
+    """Whether ``linear`` would put a product of this many rows with this weight on the weight-streaming kernel."""
+    return (rows <= SMALL_M_ROWS and weight.dtype == torch.bfloat16 and K % 8 == 0 and weight.stride(-1) == 1
+            and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, residual: torch.Tensor | None = None,
+           next_norm: tuple | None = None):
     """y = x W^T with W [out, in] (src/layer/linear.cpp:213).  A bfloat16 weight runs on tensor cores with
     32-bit accumulation: up to SMALL_M_ROWS rows on the weight-streaming kernel, more on cuBLAS.  A float32
-    weight runs on the fp32-FMA kernel, whatever the activation dtype."""
+    weight runs on the fp32-FMA kernel, whatever the activation dtype.
+    ``x`` may be ``NormedRows``: the weight-streaming kernel finishes the norm itself, otherwise it is computed
+    first.  ``residual`` (float32 [rows, out]): where the weight-streaming kernel runs, y is added to it in
+    place and None is returned - or, with ``next_norm`` = (weight, eps, owner) of the RMSNorm that follows, the
+    ``NormedRows`` that its consumer takes; otherwise y is returned and the caller adds it."""
+    if isinstance(x, NormedRows):
+        sc = x.scaled
+        if (x._value is None and small_m_usable(sc.shape[0], sc.shape[1], weight) and residual is None
+                and (out_dtype or torch.bfloat16) in (torch.bfloat16, torch.float32)):
+            return gemm_small_m(sc, weight, out_dtype or torch.bfloat16, row_ssq=(x.partials, x.eps))
+        x = x.materialize()
     _need_cuda(x, weight)
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32:
@@ -451,9 +522,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if weight.dtype != torch.bfloat16:
         raise KernelError(f"weights must be bfloat16 or float32, not {weight.dtype}")
     xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
-    if (xb.shape[0] <= SMALL_M_ROWS and xb.shape[1] % 8 == 0 and xb.stride(-1) == 1 and xb.stride(0) % 8 == 0
-            and weight.stride(-1) == 1 and weight.stride(0) % 8 == 0 and xb.data_ptr() % 16 == 0
-            and weight.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32)):
+    if (small_m_usable(xb.shape[0], xb.shape[1], weight) and xb.stride(-1) == 1 and xb.stride(0) % 8 == 0
+            and xb.data_ptr() % 16 == 0 and out_dtype in (torch.bfloat16, torch.float32)):
+        if residual is not None:
+            if next_norm is not None and out_dtype == torch.bfloat16 and FUSE_NORMS:
+                nw, eps, owner = next_norm
+                _, scaled, partials = gemm_small_m(xb, weight, torch.float32, residual=residual, emit_norm=nw)
+                return NormedRows(residual, nw, eps, out_dtype, scaled, partials, owner)
+            gemm_small_m(xb, weight, torch.float32, residual=residual)
+            return None
         return gemm_small_m(xb, weight, out_dtype)
     if out_dtype == torch.bfloat16:
         return torch.mm(xb, weight.t())

@@ -82,9 +82,14 @@ class Attention(Mixer):
     def first_weights(self):
         return self.qkv
 
-    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
-        """x [T, H] in the activation dtype; ``cache`` is the view of this execution's cache
-        (key pool, value pool, block table of its group)."""
+    takes_deferred_norm = True
+    adds_to_residual = True
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor | None = None, next_norm=None):
+        """x [T, H] in the activation dtype (or ``ops.NormedRows``: a norm that the first product finishes);
+        ``cache`` is the view of this execution's cache (key pool, value pool, block table of its group).
+        With ``residual`` the output product may add its result there and return None, or the input it
+        prepared for ``next_norm``."""
         nkv_written = self.num_kv_heads if self.writes_cache else 0
         qkv = ops.linear(x, self.qkv, ctx.act_dtype)
         rot = ctx.position_data.get(self.position) if self.position else None
@@ -109,4 +114,4 @@ class Attention(Mixer):
                 qkv, q_stride, cache.keys, cache.values, cache.block_table, ctx.token_slot, ctx.positions,
                 ctx.num_tokens, self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window,
                 self.scale)
-        return ops.linear(attn, self.o, ctx.act_dtype)
+        return ops.linear(attn, self.o, ctx.act_dtype, residual=residual, next_norm=next_norm)

@@ -65,6 +65,13 @@ class Part:
 
 
 class Mixer(Part):
+    # Two optional abilities that a block makes use of when a part declares them:
+    # takes_deferred_norm: forward() accepts ``ops.NormedRows`` for x (a norm that the first product finishes itself)
+    # adds_to_residual: forward(..., residual=h, next_norm=(weight, eps, owner) or None) may add its output to the
+    #     float32 residual h itself; it then returns None, or the ``ops.NormedRows`` prepared for ``next_norm``
+    takes_deferred_norm = False
+    adds_to_residual = False
+
     def cache_spec(self) -> CacheSpec | None:
         return None
 
@@ -76,6 +83,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_deferred_norm = False      # as for mixers
+    adds_to_residual = False
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
 
@@ -90,6 +100,11 @@ class Norm(Part):
         ``upcoming``: weights the next product will stream (a prefetch hint, may be ignored)."""
         raise NotImplementedError
 
+    def fusable(self):
+        """(weight, eps) if this norm is x * rsqrt(mean(x^2) + eps) * weight, so that the products around it can
+        prepare and finish it (see ``ops.NormedRows``); None otherwise (the default)."""
+        return None
+
 
 class PositionEncoding(Part):
     def prepare(self, ctx):
@@ -101,6 +116,10 @@ class Block(Part):
     def forward(self, stream, ctx, cache) -> None:
         raise NotImplementedError
 
+    def first_norm(self):
+        """The norm this block applies to the stream first, if it starts with one (a hint for the block before)."""
+        return None
+
 
 @dataclass
 class ResidualStream:
@@ -108,6 +127,8 @@ class ResidualStream:
     fused into the next norm (or into the final gather)."""
     hidden: torch.Tensor                 # fp32 [T, H]
     pending: torch.Tensor | None = None  # [T, H] activation dtype
+    prepared: object | None = None       # ops.NormedRows: the next norm's input, made by the product that added last
+    next_norm: object | None = None      # the norm that the next block applies first (set by the model's loop)
 
 
 # ---- registries -----------------------------------------------------------------------------------

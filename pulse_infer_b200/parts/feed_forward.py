@@ -43,14 +43,26 @@ class SwiGLU(FeedForward):
     def first_weights(self):
         return self.gate_up
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    takes_deferred_norm = True
+    adds_to_residual = True
+
+    def forward(self, x, ctx, residual: torch.Tensor | None = None, next_norm=None):
+        """With ``residual`` the down product may add its result there and return None, or the input it prepared
+        for ``next_norm``."""
+        if isinstance(x, ops.NormedRows):
+            sc = x.scaled
+            if x._value is None and self.blocked and ops.small_m_usable(sc.shape[0], sc.shape[1], self.gate_up):
+                # the norm's scale, both products and SiLU * up in one kernel
+                act = ops.gemm_small_m(sc, self.gate_up, torch.bfloat16, gated=True, row_ssq=(x.partials, x.eps))
+                return ops.linear(act, self.down, ctx.act_dtype, residual=residual, next_norm=next_norm)
+            x = x.materialize()
         fused = (self.blocked and self.gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
-                 and self.hidden_size % 8 == 0 and x.stride(-1) == 1 and x.stride(0) % 8 == 0)
+                 and self.hidden_size % 8 == 0 and x.stride(-1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
         if fused and x.shape[0] > ops.kernels.SMALL_M_ROWS:
             act = ops.gemm_tcgen05(x, self.gate_up, torch.bfloat16, gated=True)      # product + SiLU * up in one kernel
-        elif fused:
+        elif fused and ops.small_m_usable(x.shape[0], self.hidden_size, self.gate_up):
             act = ops.gemm_small_m(x, self.gate_up, torch.bfloat16, gated=True)      # the same for a few rows
         else:
             gu = ops.linear(x, self.gate_up, ctx.act_dtype)
             act = ops.silu_mul(gu, prefetch=ctx.prefetch(self.down), blocked=self.blocked)
-        return ops.linear(act, self.down, ctx.act_dtype)
+        return ops.linear(act, self.down, ctx.act_dtype, residual=residual, next_norm=next_norm)

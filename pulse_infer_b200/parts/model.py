@@ -133,8 +133,10 @@ class DecoderModel:
         ctx.position_data = {name: pe.prepare(ctx) for name, pe in self.positions.items()}
         hidden = self.embedding.forward(ctx.tokens, ctx)
         stream = ResidualStream(hidden, None)
-        for entry in self.order:
+        for i, entry in enumerate(self.order):
             block = self.layers[entry.layer]
+            following = self.layers[self.order[i + 1].layer] if i + 1 < len(self.order) else None
+            stream.next_norm = following.first_norm() if following is not None else None
             cache = ctx.cache_view(entry.cache, entry.layer) if (entry.cache is not None or
                                                                 block.mixer.state_spec() is not None) else None
             block.forward(stream, ctx, cache)

@@ -32,3 +32,6 @@ class RMSNorm(Norm):
     def add_norm(self, residual: torch.Tensor, delta, ctx, rows=None, upcoming=None) -> torch.Tensor:
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.act_dtype, rows=rows,
                                prefetch=ctx.prefetch(upcoming))
+
+    def fusable(self):
+        return self.weight, self.eps

@@ -326,6 +326,52 @@ def test_gemm_small_m_gated_epilogue(M, I, K):
     assert np.abs(two.double().numpy() - want).max() <= 2 ** -6 * np.abs(want).max() + 1e-6
 
 
+@pytest.mark.parametrize("M,H,N,K", [(1, 4096, 6144, 1024), (8, 200, 515, 96), (16, 1024, 4096, 520), (13, 48, 224, 4104), (5, 16, 16, 8)])
+@pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float32])
+def test_gemm_small_m_prepares_and_finishes_a_norm(M, H, N, K, wdt):
+    """h += a W1^T as the epilogue of a product that also prepares the RMSNorm of the new h; the next product
+    finishes that norm: norm(h) W2^T, plain and with SiLU * up behind it.  Each against float64."""
+    dev, ops = need_gpu(), _ops()
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    w1 = (torch.randn(H, K, generator=g) * 0.3).to(torch.bfloat16)
+    h0 = torch.randn(M + 2, H + 8, generator=g) * 3
+    h0[1] *= 40.0                                             # rows of very different size: the scale is per row
+    nw = (1 + 0.2 * torch.randn(H, generator=g)).to(wdt)
+    w2 = (torch.randn(N, H, generator=g) * 0.3).to(torch.bfloat16)
+    eps = 1e-5
+    # the residual epilogue alone: r += x W^T in 32-bit, nothing else touched
+    hd = h0.clone().to(dev)
+    assert ops.linear(a.to(dev), w1.to(dev), torch.bfloat16, residual=hd[1:M + 1, :H]) is None
+    want_h = h0.double()
+    want_h[1:M + 1, :H] += a.double() @ w1.double().t()
+    bound = 4e-6 * float((a.abs().double() @ w1.abs().double().t()).max() + h0.abs().max()) + 1e-6
+    assert float((hd.cpu().double() - want_h).abs().max()) <= bound
+    assert torch.equal(hd.cpu()[0], h0[0]) and torch.equal(hd.cpu()[:, H:], h0[:, H:])
+    # with the next norm prepared: the same residual, and a description that the next product finishes
+    hd2 = h0[1:M + 1, :H].contiguous().to(dev)
+    owner = object()
+    rows = ops.linear(a.to(dev), w1.to(dev), torch.bfloat16, residual=hd2, next_norm=(nw.to(dev), eps, owner))
+    assert isinstance(rows, ops.NormedRows) and rows.owner is owner and torch.equal(hd2.cpu(), hd.cpu()[1:M + 1, :H])
+    normed = plain_model.rms_norm(want_h[1:M + 1, :H].numpy(), nw.double().numpy(), eps)
+    want = normed @ w2.double().numpy().T
+    out = ops.linear(rows, w2.to(dev), torch.bfloat16).cpu()
+    assert out.dtype == torch.bfloat16 and np.abs(out.double().numpy() - want).max() <= 2 ** -7 * np.abs(want).max() + 1e-6
+    # the unfused route (norm kernel, then the product) agrees to bf16 rounding, and materialize() is that norm
+    x = rows.materialize()
+    assert np.abs(x.cpu().double().numpy() - normed).max() <= 2 ** -8 * np.abs(normed).max()
+    two = ops.gemm_small_m(x, w2.to(dev), torch.bfloat16).cpu()
+    assert np.abs(two.double().numpy() - want).max() <= 2 ** -6 * np.abs(want).max() + 1e-6
+    if N % 16 == 0:                                           # finishing the norm + gated epilogue
+        I = N // 2
+        want_g = plain_model.silu(normed @ w2[:I].double().numpy().T) * (normed @ w2[I:].double().numpy().T)
+        wi = ops.interleave_gate_up(w2[:I].contiguous().to(dev), w2[I:].contiguous().to(dev))
+        got = ops.gemm_small_m(rows.scaled, wi, torch.bfloat16, gated=True, row_ssq=(rows.partials, rows.eps)).cpu()
+        # gate and up each carry the rounding of the bf16 inputs (2^-9 an element, not averaged out when H is 16),
+        # their product carries both, and the result is rounded once more
+        assert got.shape == (M, I) and np.abs(got.double().numpy() - want_g).max() <= 2 ** -6 * np.abs(want_g).max() + 1e-6
+
+
 @pytest.mark.parametrize("M,I,K", [(200, 224, 192), (130, 200, 64)])
 def test_gemm_tcgen05_gated_epilogue(M, I, K):
     dev, ops = need_gpu(), _ops()
