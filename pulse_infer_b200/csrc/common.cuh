@@ -52,7 +52,7 @@ PI_EXPORT const char* pi_last_error() { return g_pi_error; }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Which kernels let their successor be scheduled early (bit mask): 1 small kernels, 2 products, 4 attention.
 #ifndef PI_PDL_EARLY
-#define PI_PDL_EARLY 1
+#define PI_PDL_EARLY 3
 #endif
 #define PDL_SMALL 1
 #define PDL_PRODUCT 2

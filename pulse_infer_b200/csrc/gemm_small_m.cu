@@ -10,8 +10,11 @@
 // Wide outputs (thousands of 16-feature tiles) use 8 warps per CTA with two register sets of weights in
 // flight; narrow ones (N = 4096 gives only 256 tiles) use 16 warps per CTA so that the whole GPU still has
 // loads in flight.
-// (Splitting K further across the CTAs of a thread-block cluster, reduced through distributed shared memory,
-// was measured and dropped: it made the 33-100 MB products of a decode step slower, not faster.)
+// (Measured and dropped: splitting K further across the CTAs of a thread-block cluster, reduced through
+// distributed shared memory - the 33-100 MB products of a decode step got slower; applying the whole RMSNorm
+// inside the product from the 32-bit residual - every CTA then reads twice the activation bytes and does the
+// norm's arithmetic in its inner loop, 34 -> 52 us for the gate_up product; prefetching a CTA's whole tile into
+// L2 before the wait on the previous kernel - 8 % slower steps.)
 //
 // Within a 32-wide block of k, thread t of a quad supplies elements 8t..8t+7 of its row for both operands:
 // 8t+0..3 go to the four k slots that the thread owns in the first mma, 8t+4..7 to those of the second.  The
