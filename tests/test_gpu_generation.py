@@ -316,6 +316,154 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     assert np.abs(logits - want["b"]).max() <= 2e-5 * np.abs(want["b"]).max()
 
 
+# ---- a toy feed-forward with routing and a toy position encoding, registered from the test ------------------------
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):
+    """A new architecture: the first layer's feed-forward routes every token to one of four small experts
+    (router logits and softmax in 32-bit, top 1), and positions rotate only the first half of each head, with
+    angles that grow linearly in the pair index and 'half' pairing.  Both parts, the architecture and its
+    configuration are registered here; nothing under pulse_infer_b200/ is changed."""
+    dev = need_gpu()
+    from pulse_infer_b200.config import Qwen3Config, register_architecture
+    from pulse_infer_b200.engine import Segment, build_runner
+    from pulse_infer_b200.models.qwen3 import build_qwen3_spec
+    from pulse_infer_b200.models.spec import PartSpec
+    from pulse_infer_b200.parts.base import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding, TensorSpec,
+                                             register_part)
+    from pulse_infer_b200.weights import write_random_model
+
+    EXPERTS, WIDTH, ALPHA = 4, 40, 0.013
+
+    class Top1Experts(FeedForward):
+        """y = p_e * W_out[e] relu(W_in[e] x), e = argmax of the router's logits, p = their softmax."""
+
+        def __init__(self, hidden_size, experts, width):
+            self.hidden_size, self.experts, self.width = hidden_size, experts, width
+
+        def tensor_specs(self):
+            specs = {"router.weight": TensorSpec((self.experts, self.hidden_size))}
+            for e in range(self.experts):
+                specs[f"experts.{e}.in.weight"] = TensorSpec((self.width, self.hidden_size))
+                specs[f"experts.{e}.out.weight"] = TensorSpec((self.hidden_size, self.width))
+            return specs
+
+        def load(self, tensors, runtime):
+            self.router = tensors["router.weight"].float()
+            self.w_in = torch.stack([tensors[f"experts.{e}.in.weight"].float() for e in range(self.experts)])
+            self.w_out = torch.stack([tensors[f"experts.{e}.out.weight"].float() for e in range(self.experts)])
+            self._tensors = {"router": self.router, "w_in": self.w_in, "w_out": self.w_out}
+
+        def first_weights(self):
+            return None
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            probs = torch.softmax(xf @ self.router.t(), dim=-1)
+            p, e = probs.max(dim=-1)
+            hid = torch.relu(torch.einsum("tfh,th->tf", self.w_in[e], xf))
+            return (torch.einsum("thf,tf->th", self.w_out[e], hid) * p[:, None]).to(x.dtype)
+
+    class LinearRotary(PositionEncoding):
+        """angle(pos, i) = pos * alpha * (i + 1) for pair i of the first ``rotary_dim`` elements, pairs (i, i + rot/2)."""
+
+        def __init__(self, alpha, rotary_dim):
+            self.alpha, self.rotary_dim = alpha, rotary_dim
+
+        def prepare(self, ctx):
+            i = torch.arange(1, self.rotary_dim // 2 + 1, dtype=torch.float64, device=ctx.positions.device)
+            ang = ctx.positions.double()[:, None] * (self.alpha * i)[None, :]
+            return {"cos": torch.cos(ang).float().contiguous(), "sin": torch.sin(ang).float().contiguous(), "adjacent": False}
+
+    if "top1_experts" not in FEED_FORWARDS:
+        register_part("feed_forward", "top1_experts")(Top1Experts)
+    if "linear_rotary" not in POSITION_ENCODINGS:
+        register_part("position_encoding", "linear_rotary")(LinearRotary)
+
+    @dataclasses.dataclass(frozen=True)
+    class RoutedConfig(Qwen3Config):
+        pass
+
+    def build_routed_spec(config):
+        spec = build_qwen3_spec(config)
+        layers = list(spec.layers)
+        layers[0] = dataclasses.replace(layers[0], feed_forward=PartSpec(
+            "top1_experts", dict(hidden_size=config.hidden_size, experts=EXPERTS, width=WIDTH), "model.layers.0.moe."))
+        positions = {"rotary": PartSpec("linear_rotary", dict(alpha=ALPHA, rotary_dim=config.head_dim // 2))}
+        return dataclasses.replace(spec, layers=tuple(layers), positions=positions)
+
+    register_architecture("RoutedForCausalLM", RoutedConfig, build_routed_spec, replace=True)
+    base = CONFIGS["B"]
+    cfg = RoutedConfig(**{**{f.name: getattr(base, f.name) for f in dataclasses.fields(base)},
+                          "architecture": "RoutedForCausalLM"})
+    folder = write_random_model(cfg, 11, str(tmp_path / "routed"), dtype="bfloat16")
+    pc, pw = load_plain(folder)
+    assert "model.layers.0.moe.router.weight" in pw and "model.layers.0.mlp.gate_proj.weight" not in pw
+
+    def toy_rope(x, positions):
+        rot = pc["head_dim"] // 2
+        pairs = rot // 2
+        ang = np.asarray(positions, dtype=np.float64)[:, None] * (ALPHA * np.arange(1, pairs + 1))[None, :]
+        cos, sin = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+        out = x.copy()
+        a, b = x[..., :pairs], x[..., pairs:rot]
+        out[..., :pairs] = a * cos - b * sin
+        out[..., pairs:rot] = a * sin + b * cos
+        return out
+
+    margins = []
+
+    def plain_routed(tokens):
+        w = {k: np.asarray(v, dtype=np.float64) for k, v in pw.items()}
+        T, positions = len(tokens), np.arange(len(tokens))
+        nq, nkv, d, eps = pc["num_attention_heads"], pc["num_key_value_heads"], pc["head_dim"], pc["rms_norm_eps"]
+        h = plain_model.embedding(w["model.embed_tokens.weight"], tokens)
+        for layer in range(pc["num_hidden_layers"]):
+            pre = f"model.layers.{layer}."
+            x = plain_model.rms_norm(h, w[pre + "input_layernorm.weight"], eps)
+            q = plain_model.linear(x, w[pre + "self_attn.q_proj.weight"]).reshape(T, nq, d)
+            k = plain_model.linear(x, w[pre + "self_attn.k_proj.weight"]).reshape(T, nkv, d)
+            v = plain_model.linear(x, w[pre + "self_attn.v_proj.weight"]).reshape(T, nkv, d)
+            q = toy_rope(plain_model.rms_norm(q, w[pre + "self_attn.q_norm.weight"], eps), positions)
+            k = toy_rope(plain_model.rms_norm(k, w[pre + "self_attn.k_norm.weight"], eps), positions)
+            h = h + plain_model.linear(plain_model.attention(q, k, v).reshape(T, nq * d), w[pre + "self_attn.o_proj.weight"])
+            x = plain_model.rms_norm(h, w[pre + "post_attention_layernorm.weight"], eps)
+            if layer == 0:
+                logits = x @ w[pre + "moe.router.weight"].T
+                srt = np.sort(logits, axis=-1)
+                margins.append(float((srt[:, -1] - srt[:, -2]).min()))
+                y = np.zeros_like(h)
+                for t in range(T):
+                    e = int(np.argmax(logits[t]))
+                    p = plain_model.softmax(logits[t])[e]
+                    hid = np.maximum(w[pre + f"moe.experts.{e}.in.weight"] @ x[t], 0.0)
+                    y[t] = p * (w[pre + f"moe.experts.{e}.out.weight"] @ hid)
+                h = h + y
+            else:
+                h = h + plain_model.swiglu(x, w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"],
+                                           w[pre + "mlp.down_proj.weight"])
+        x = plain_model.rms_norm(h, w["model.norm.weight"], eps)
+        return plain_model.linear(x, w["lm_head.weight"])
+
+    reqs = {"a": random_tokens(4, 45, cfg.vocab_size), "b": random_tokens(5, 19, cfg.vocab_size)}
+    want = {k: plain_routed(v) for k, v in reqs.items()}
+    assert min(margins) > 1e-4, "a router decision of this seed is too close to call; pick another seed"
+    runner = build_runner(folder, dtype="float32", device="cuda:0", page_size=8, num_pages=32, max_requests=2,
+                          max_tokens_per_request=128)
+    runner.open("a"); runner.open("b")
+    plan = [[("a", 0, 17), ("b", 0, 2)], [("a", 17, 18), ("b", 2, 19)], [("a", 18, 45)]]
+    for step in plan:
+        logits = runner.step([Segment(r, reqs[r][a:b], list(range(b - a))) for r, a, b in step]).cpu().double().numpy()
+        ref = np.concatenate([want[r][a:b] for r, a, b in step])
+        assert np.abs(logits - ref).max() <= 2e-5 * np.abs(ref).max()
+    # the same model in bfloat16 steps too (routing may differ there, so only the shape and finiteness are checked)
+    runner16 = build_runner(folder, dtype="bfloat16", device="cuda:0", page_size=8, num_pages=32, max_requests=2,
+                            max_tokens_per_request=128)
+    runner16.open("a")
+    out = runner16.step([Segment("a", reqs["a"][:20], [19])])
+    out = runner16.step([Segment("a", reqs["a"][20:21], [0])])
+    assert out.shape == (1, cfg.vocab_size) and bool(torch.isfinite(out).all())
+    runner16.check_device_errors()
+
+
 def test_layer_order_as_data_repeat_and_shared_cache(model_folders, tmp_path):
     """The order in which layers run is a list: here layer 0 runs twice (with a cache of its own each
     time) and a last layer without key/value projections reads the cache that layer 1 filled."""
