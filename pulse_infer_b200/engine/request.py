@@ -22,7 +22,7 @@ class RequestState(Enum):
     FINISHED = "finished"
 
 
-@dataclass
+@dataclass(eq=False)        # a request is itself, not its field values: the scheduler's lists compare by identity
 class InferenceRequest:
     request_id: int
     prompt_tokens: list
