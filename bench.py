@@ -329,7 +329,7 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a C++/CMake project without setup.py or "
-                          "pyproject.toml: 'pip install --no-index ... /root/reference' answers 'not installable', and its "
+                          "pyproject.toml: 'pip install --no-index --target baseline/_ref <the reference>' answers 'not installable', and its "
                           "CMake build fetches spdlog/json/googletest from the network"}))
         return 0
     if args.gpus != 1:

@@ -61,7 +61,7 @@ def build_driver(reference: str, workdir: str) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     out_dir = os.path.dirname(os.path.abspath(__file__))
     with tempfile.TemporaryDirectory() as work:
