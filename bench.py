@@ -131,7 +131,8 @@ def prefill_flops(cfg, T: int) -> float:
     return linear + attention
 
 
-def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: bool, context: int | None = None):
+def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: bool, context: int | None = None,
+                 prompt: int | None = None):
     """``steps`` timed decode steps of ``batch`` requests whose prompts were 2,048 random ids, ending at
     context 4096.  through_api=False: the step function with device-side argmax and pre-drawn input
     tokens (no host round trip between steps).  through_api=True: Engine.step() - every step takes host
@@ -144,6 +145,7 @@ def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: 
     vocab = engine.config.vocab_size
     runner = engine.runner
     CONTEXT = context or globals()["CONTEXT"]
+    PROMPT = prompt or globals()["PROMPT"]
     prompts = [[int(t) for t in rng.randint(0, vocab, size=PROMPT)] for _ in range(batch)]
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     h2d = StepContext.layout(batch, batch, batch)["_total"][1] * 4
@@ -204,10 +206,11 @@ def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: 
     return ms, launches, mean_ctx, h2d, d2h
 
 
-def timed_prefill(engine, rng, repeats: int = 3):
+def timed_prefill(engine, rng, repeats: int = 3, prompt: int | None = None):
     import torch
     from pulse_infer_b200.engine import Segment
     runner = engine.runner
+    PROMPT = prompt or globals()["PROMPT"]
     tokens = [int(t) for t in rng.randint(0, engine.config.vocab_size, size=PROMPT)]
     times = []
     for i in range(repeats + 1):
@@ -228,11 +231,12 @@ def timed_prefill(engine, rng, repeats: int = 3):
     return statistics.median(times)
 
 
-def make_engine(cfg, max_batch: int, graphs: bool = True):
+def make_engine(cfg, max_batch: int, graphs: bool = True, context: int | None = None, prompt: int | None = None):
     from pulse_infer_b200 import Engine
-    return Engine(None, config=cfg, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=max_batch * (CONTEXT + 256),
-                  max_batch_size=max_batch, chunk_size=PROMPT, max_tokens_per_step=PROMPT + max_batch,
-                  max_tokens_per_request=CONTEXT + 256, use_cuda_graphs=graphs)
+    context, prompt = context or CONTEXT, prompt or PROMPT
+    return Engine(None, config=cfg, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=max_batch * (context + 256),
+                  max_batch_size=max_batch, chunk_size=prompt, max_tokens_per_step=prompt + max_batch,
+                  max_tokens_per_request=context + 256, use_cuda_graphs=graphs)
 
 
 def run_part(args) -> dict:
@@ -242,13 +246,19 @@ def run_part(args) -> dict:
     PROFILER_RANGE = True
     cfg = make_config(args.layers or FULL_LAYERS)
     rng = np.random.RandomState(0)
-    engine = make_engine(cfg, args.batch, graphs=not args.no_graphs)
     if args.only == "prefill":
-        ms = timed_prefill(engine, rng, repeats=max(1, args.steps))
-        return {"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": PROMPT, "ms": round(ms, 3)}
-    ms, launches, ctx, _, _ = timed_decode(engine, args.batch, args.steps, args.warmup, rng, False, context=args.context)
+        T = args.prompt_len or PROMPT
+        engine = make_engine(cfg, args.batch, graphs=not args.no_graphs, context=max(CONTEXT, T), prompt=T)
+        ms = timed_prefill(engine, rng, repeats=max(1, args.steps), prompt=T)
+        return {"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": T, "ms": round(ms, 3),
+                "tokens_per_s": round(T / ms * 1e3, 1)}
+    prompt = args.prompt_len or min(PROMPT, args.context - args.steps - args.warmup - 1)
+    engine = make_engine(cfg, args.batch, graphs=not args.no_graphs, context=args.context, prompt=prompt)
+    ms, launches, ctx, _, _ = timed_decode(engine, args.batch, args.steps, args.warmup, rng, False, context=args.context,
+                                           prompt=prompt)
     return {"only": "decode", "layers": cfg.num_hidden_layers, "batch": args.batch, "context": args.context,
-            "ms_per_step": round(ms, 4), "gpu_launches": launches, "cuda_graphs": not args.no_graphs}
+            "ms_per_step": round(ms, 4), "tokens_per_s": round(args.batch / ms * 1e3, 1), "gpu_launches": launches,
+            "cuda_graphs": not args.no_graphs}
 
 
 def run_ours(args) -> dict:
@@ -325,6 +335,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the 36 of the shape (named in config)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one phase only (for profilers)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: the context the timed steps end at")
+    ap.add_argument("--prompt-len", type=int, default=None, help="with --only: tokens of each prompt (default 2048)")
     ap.add_argument("--no-graphs", action="store_true", help="with --only: launch decode steps eagerly")
     args = ap.parse_args()
     if args.impl == "reference":

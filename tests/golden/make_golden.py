@@ -7,7 +7,7 @@ the tiny models A and B with this framework's seeded random-weights mode (stored
 rounded to bfloat16 first so that both precisions of the engine load the same numbers), runs the driver
 on fixed prompts and stores tokens and logits in ``tiny_<name>.npz``.
 
-Run from the repository root:  python tests/golden/make_golden.py [--reference /path/to/pulse_infer]
+Run from the repository root:  python tests/golden/make_golden.py --reference /path/to/pulse_infer
 The reference requires ``lm_head.weight`` even for a tied model (src/model/qwen3/model.cpp:1009-1021), so
 the copy of the folder that the driver reads gets one equal to the embedding.
 """
