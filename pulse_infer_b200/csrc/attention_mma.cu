@@ -765,7 +765,8 @@ PI_EXPORT int pi_attention_num_splits(int pos, int window, int split_keys) {
 // present); max_seg_len bounds the grid of the prompt kernel; max_splits is the width of the scratch and the
 // grid depth of the decode kernel (>= the number of ranges of every decoding request in the batch).
 // prefetch_ptr / prefetch_bytes: weights the next product will stream; the merge kernel's spare CTAs ask for them
-// to be brought into L2 (null / 0: none)
+// to be brought into L2 (null / 0: none).  has_decode = 2: the partial results of the key ranges are already in
+// part_acc / part_ml (written by the tcgen05 decode kernel); only the merge runs.
 PI_EXPORT int pi_attention_mma_prefetch(const void* q, int q_stride, const void* kcache, const void* vcache,
                                const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
                                const int* seg_start, const int* seg_len, const int* token_seg, void* out,
@@ -807,12 +808,14 @@ PI_EXPORT int pi_attention_mma_prefetch(const void* q, int q_stride, const void*
         if (max_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return pi_refuse("pi_attention_mma: scratch for %d key ranges is missing", max_splits);
         p.decode = 1;
         p.tiles_per_seg = (p.group + 15) / 16;
+        if (has_decode == 2) {
+            // the partial results were written by another kernel (same layout): only the merge runs here
+        } else
 #if PI_HEAD_DIM % 32 == 0
-        const bool contig = page_size % 16 == 0;
-        if (p.group <= 8) rc = contig ? launch_attn_decode<1, true>(p, num_segments, max_splits, stream)
-                                      : launch_attn_decode<1, false>(p, num_segments, max_splits, stream);
-        else if (p.group <= 16) rc = contig ? launch_attn_decode<2, true>(p, num_segments, max_splits, stream)
-                                            : launch_attn_decode<2, false>(p, num_segments, max_splits, stream);
+        if (p.group <= 8) rc = page_size % 16 == 0 ? launch_attn_decode<1, true>(p, num_segments, max_splits, stream)
+                                                   : launch_attn_decode<1, false>(p, num_segments, max_splits, stream);
+        else if (p.group <= 16) rc = page_size % 16 == 0 ? launch_attn_decode<2, true>(p, num_segments, max_splits, stream)
+                                                         : launch_attn_decode<2, false>(p, num_segments, max_splits, stream);
         else rc = launch_attn<1, 4, 3>(p, num_segments, max_splits, stream);
 #else
         rc = launch_attn<1, 4, 3>(p, num_segments, max_splits, stream);

@@ -495,6 +495,375 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
 }
 
+// =============================================================================================================
+// Decode: segments of one token.  The work is all memory traffic - every key and value of the request is read
+// once for a handful of query rows - so the kernel is built around keeping HBM busy: a persistent CTA per SM
+// walks a list of (request, kv head, key range) items, and its TMA producer warp runs ahead through a ring of
+// key/value tiles ACROSS item boundaries, so the ring never drains while an item finishes.
+//   S^T = K Q^T     tcgen05.mma M 128 (keys of the tile) x N 16 (the group's query heads, padded): the key tile
+//                   that TMA delivered is the A operand as it lies; the scores land in tensor memory with one
+//                   key per lane
+//   softmax         four warps, thread = key: column maxima by warp shuffles and one exchange through shared
+//                   memory per tile; every thread keeps the running maxima (the same in all threads) and the
+//                   sum over ITS keys, which is reduced across threads once per item
+//   O^T += V^T P^T  tcgen05.mma M 128 (head dimension) x N 16, A = the value tile MN-major, B = the
+//                   probabilities [16 heads, 128 keys] from shared memory
+// An item with the only key range of its request writes the output; otherwise it writes (max, sum, accumulator)
+// in the layout attn_merge_kernel of attention_mma.cu combines.  Key ranges are those of the mma.sync decode
+// kernel: they depend on the request's own length only.
+// Needs a group of at most 16 query heads per kv head and pages of at most 64 keys.
+// Measured (Qwen3-8B sizes, 36 layers): 4.62 ms a step against 4.15 ms with the mma.sync decode kernel at batch 8,
+// 11.7 against 11.3 at batch 64, 10.7 against 10.5 at batch 8 and 32k context.  The cycle counters (-DFA_PROFILE)
+// show why: with ranges of 256 keys an item is two tiles, and per item the chain costs about 3,000 cycles waiting
+// for its queries, 3,500 per tile in the softmax warps (loads, shuffles for the column maxima, exchange, exponentials)
+// and 3,000 for the output - 7 us for 128 KB, where one SM's share of HBM would deliver them in under 3 us.  The
+// mma.sync kernel hides the same latencies behind four resident CTAs per SM.  The kernel is therefore not the
+// default (PULSE_TCGEN05_DECODE=1 selects it); what it needs next is two item streams per CTA and the queries of
+// the next item loaded ahead.
+// =============================================================================================================
+#define FD_THREADS 192
+#define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
+
+struct FdParams {
+    const bf16* q; int q_stride;
+    const int* block_table; int bt_stride;
+    const int* seg_off; const int* seg_slot; const int* seg_start; const int* seg_len;
+    bf16* out; float* part_acc; float* part_ml; int max_splits;
+    int nq, nkv, group;
+    int page_size, window;
+    float scale_log2;
+    int num_segments, split_keys, num_items;
+};
+
+struct FdItem {
+    int seg, kvh, split, nsplits, pos, lo, kb, ke, ntiles;
+};
+
+// item `it` of the box [max_splits][segments][kv heads] (key ranges slowest, so that the items that exist come first)
+__device__ __forceinline__ bool fd_item(const FdParams& p, int it, FdItem& w) {
+    w.kvh = it % p.nkv;
+    const int rest = it / p.nkv;
+    w.seg = rest % p.num_segments;
+    w.split = rest / p.num_segments;
+    if (p.seg_len[w.seg] != 1) return false;
+    w.pos = p.seg_start[w.seg];
+    w.lo = fa_window_lo(w.pos, p.window);
+    const int lo_al = (w.lo / 64) * 64;
+    w.nsplits = (w.pos + 1 - lo_al + p.split_keys - 1) / p.split_keys;
+    if (w.split >= w.nsplits) return false;
+    w.kb = lo_al + w.split * p.split_keys;
+    w.ke = min(w.kb + p.split_keys, w.pos + 1);
+    w.ntiles = (w.ke - w.kb + FA_BN - 1) / FA_BN;
+    return true;
+}
+
+__device__ __forceinline__ void fa_tmem_ld16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fd_softmax_sync() {       // the four softmax warps
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(FD_THREADS, 1)
+attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const FdParams p) {
+    constexpr int HALVES = D / 64;
+    constexpr unsigned HALF_BYTES = 128 * 128;            // a 64-wide half of a key / value tile: 128 rows x 128 bytes
+    constexpr unsigned TILE_BYTES = HALVES * HALF_BYTES;
+    constexpr unsigned STAGE_BYTES = 2 * TILE_BYTES;      // keys, then values
+    constexpr unsigned QHALF_BYTES = 16 * 128;            // 16 query rows x 128 bytes
+    constexpr unsigned PHALF_BYTES = 16 * 128;            // 16 rows of probabilities x 64 keys
+    constexpr unsigned TMEM_COLS = 64;                    // S^T twice (16 columns each), O^T (16 columns)
+    constexpr unsigned O_COL = 32;
+    constexpr int STAGES = FD_STAGES;
+
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sKV = smem;                                        // [STAGES][K tile | V tile]
+    unsigned char* sQ = sKV + STAGES * STAGE_BYTES;                   // [HALVES][16 rows][128 B]
+    unsigned char* sP = sQ + 2 * QHALF_BYTES;                         // [2 halves of keys][16 rows][128 B]
+    float* xmax = reinterpret_cast<float*>(sP + 2 * PHALF_BYTES);     // [2 parities][4 warps][16]
+    float* xsum = xmax + 2 * 4 * 16;                                  // [4 warps][16]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(xsum + 4 * 16);
+    unsigned long long* full = bars;                      // [STAGES] TMA -> MMA
+    unsigned long long* empty = bars + STAGES;            // [STAGES] MMA -> TMA
+    unsigned long long* s_full = bars + 2 * STAGES;       // [2] MMA -> softmax: scores of a tile
+    unsigned long long* p_ready = s_full + 2;             // softmax (4 warps) -> MMA: P written, O rescaled, S read
+    unsigned long long* pv_done = s_full + 3;             // MMA -> softmax: O updated, P free
+    unsigned long long* q_ready = s_full + 4;             // softmax (4 warps) -> MMA: the item's queries are in place
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(s_full + 5);
+    volatile unsigned* failed = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.group;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { fa_mbar_init(&full[i], 1); fa_mbar_init(&empty[i], 1); }
+        fa_mbar_init(&s_full[0], 1); fa_mbar_init(&s_full[1], 1);
+        fa_mbar_init(p_ready, 4); fa_mbar_init(pv_done, 1); fa_mbar_init(q_ready, 4);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // ring, queries and probabilities start as zeros: rows that nothing fills (keys past the end of a range,
+    // query rows past the group) must not hold NaN bit patterns
+    for (unsigned i = threadIdx.x; i < (STAGES * STAGE_BYTES + 2 * QHALF_BYTES + 2 * PHALF_BYTES) / 16; i += FD_THREADS)
+        reinterpret_cast<uint4*>(sKV)[i] = make_uint4(0, 0, 0, 0);
+    pdl_wait();
+    fa_fence_async_smem();
+    fa_fence_before();
+    __syncthreads();
+    fa_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: lane = page of the key tile; runs ahead across items ----------------
+        const int ps = p.page_size, pages_per_tile = FA_BN / ps;
+        const unsigned page_bytes = (unsigned)ps * 128u;
+        int t = 0;
+        bool ok = true;
+        for (int it = blockIdx.x; it < p.num_items && ok && !*failed; it += gridDim.x) {
+            FdItem w;
+            if (!fd_item(p, it, w)) continue;
+            const int* table = p.block_table + (size_t)p.seg_slot[w.seg] * p.bt_stride;
+            for (int j = 0; j < w.ntiles; ++j, ++t) {
+                const int st = t % STAGES, use = t / STAGES;
+                const int key = w.kb + j * FA_BN + lane * ps;
+                const int page = (lane < pages_per_tile && key < w.ke) ? table[key / ps] : -1;
+                const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
+                const unsigned bytes = (unsigned)__popc(mask) * page_bytes * HALVES * 2;
+                const int row = (page * p.nkv + w.kvh) * ps;
+                FA_T0();
+                if (use > 0 && !fa_mbar_wait(&empty[st], (use - 1) & 1, (1u << 24) | t, failed)) { ok = false; break; }
+                FA_ACC(0);
+                if (lane == 0) fa_mbar_expect_tx(&full[st], bytes);
+                __syncwarp();
+                if (page >= 0) {
+                    unsigned char* dst = sKV + st * STAGE_BYTES + lane * page_bytes;
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) {
+                        fa_tma_load(dst + h * HALF_BYTES, &map_k, h * 64, row, &full[st]);
+                        fa_tma_load(dst + TILE_BYTES + h * HALF_BYTES, &map_v, h * 64, row, &full[st]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // S^T: M 128 keys x N 16 heads, both K-major.  O^T: M 128 (head dimension) x N 16, A (values) MN-major.
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+            const unsigned idesc_pv = idesc_s | (1u << 15);
+            int t = 0, ic = 0;
+            bool ok = true;
+            auto issue_s = [&](int tt) -> bool {        // scores of tile tt into buffer tt & 1
+                const int st = tt % STAGES;
+                FA_T0();
+                if (!fa_mbar_wait(&full[st], (tt / STAGES) & 1, (2u << 24) | tt, failed)) return false;
+                FA_ACC(3);
+                fa_fence_after();
+                const unsigned char* kt = sKV + st * STAGE_BYTES;
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        fa_mma(tmem_base + (tt & 1) * 16, fa_desc_kmajor(fa_smem(kt + h * HALF_BYTES) + k * 32),
+                               fa_desc_kmajor(fa_smem(sQ + h * QHALF_BYTES) + k * 32), idesc_s, (h > 0 || k > 0) ? 1u : 0u);
+                fa_commit(&s_full[tt & 1]);
+                return true;
+            };
+            for (int it = blockIdx.x; it < p.num_items && ok && !*failed; it += gridDim.x) {
+                FdItem w;
+                if (!fd_item(p, it, w)) continue;
+                FA_T0();
+                if (!fa_mbar_wait(q_ready, ic & 1, (3u << 24) | ic, failed)) break;
+                FA_ACC(4);
+                ++ic;
+                ok = issue_s(t);
+                for (int j = 0; j < w.ntiles && ok; ++j, ++t) {
+                    if (j + 1 < w.ntiles) ok = issue_s(t + 1);      // the next scores while this tile is in its softmax
+                    if (!ok) break;
+                    FA_T0();
+                    if (!fa_mbar_wait(p_ready, t & 1, (4u << 24) | t, failed)) { ok = false; break; }
+                    FA_ACC(5);
+                    fa_fence_after();
+                    const int st = t % STAGES;
+                    const unsigned char* vt = sKV + st * STAGE_BYTES + TILE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < FA_BN / 16; ++kk)
+                        fa_mma(tmem_base + O_COL, fa_desc_mnmajor(fa_smem(vt) + kk * 16 * 128, HALVES == 2 ? HALF_BYTES : 0u),
+                               fa_desc_kmajor(fa_smem(sP + (kk / 4) * PHALF_BYTES) + (kk % 4) * 32), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    fa_commit(pv_done);
+                    fa_commit(&empty[st]);        // keys and values of this stage are no longer read
+                }
+            }
+        }
+    } else {
+        // ---------------- softmax and output: thread = key (scores) / = element of the head (output) ----------------
+        const int quarter = warp & 3;
+        const int tid = quarter * 32 + lane;               // TMEM lane of this thread
+        const unsigned lane_base = (unsigned)(quarter * 32) << 16;
+        int t = 0, ic = 0;
+        bool alive = true;
+        for (int it = blockIdx.x; it < p.num_items; it += gridDim.x) {
+            FdItem w;
+            if (!fd_item(p, it, w)) continue;
+            // the item's queries: rows g < G of a [16, D] K-major tile (the previous item's products are complete)
+            const int tok = p.seg_off[w.seg];
+            for (int idx = tid; idx < G * (D / 8); idx += 128) {
+                const int g = idx / (D / 8), c = idx % (D / 8);
+                const uint4 v = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.q_stride + (size_t)(w.kvh * G + g) * D + c * 8);
+                *reinterpret_cast<uint4*>(sQ + (c / 8) * QHALF_BYTES + g * 128 + (((c % 8) ^ (g & 7)) << 4)) = v;
+            }
+            fa_fence_async_smem();
+            __syncwarp();
+            if (lane == 0) fa_mbar_arrive(q_ready);
+            ++ic;
+            float m_run[16], l_thr[16];
+#pragma unroll
+            for (int g = 0; g < 16; ++g) { m_run[g] = -INFINITY; l_thr[g] = 0.0f; }
+            for (int j = 0; j < w.ntiles; ++j, ++t) {
+                FA_T0();
+                alive = alive && fa_mbar_wait(&s_full[t & 1], (t >> 1) & 1, (5u << 24) | t, failed);
+                if (warp == 2) FA_ACC(8);
+                fa_fence_after();
+                float s[16];
+                fa_tmem_ld16(tmem_base + (t & 1) * 16 + lane_base, s);
+                const int key = w.kb + j * FA_BN + tid;
+                const bool vis = key <= w.pos && key >= w.lo && key < w.ke;
+                float wm[16];
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    s[g] = vis ? s[g] * p.scale_log2 : -INFINITY;
+                    wm[g] = s[g];
+                }
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    if (g < G) {
+#pragma unroll
+                        for (int off = 16; off > 0; off >>= 1) wm[g] = fmaxf(wm[g], __shfl_xor_sync(0xffffffffu, wm[g], off));
+                    }
+                }
+                float* xm = xmax + (t & 1) * 64;
+                if (lane < 16) {
+                    float mine = -INFINITY;
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) mine = (lane == g) ? wm[g] : mine;
+                    xm[quarter * 16 + lane] = mine;
+                }
+                if (warp == 2) FA_ACC(9);
+                fd_softmax_sync();
+                if (warp == 2) FA_ACC(10);
+                float alpha[16];
+                bool moved = false;
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    if (g < G) {
+                        const float mt = fmaxf(fmaxf(xm[g], xm[16 + g]), fmaxf(xm[32 + g], xm[48 + g]));
+                        const float m_new = fmaxf(m_run[g], mt);
+                        const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+                        alpha[g] = fa_ex2(m_run[g] - base);
+                        moved = moved || (alpha[g] != 1.0f);
+                        m_run[g] = m_new;
+                        s[g] = fa_ex2(s[g] - base);                 // -inf gives 0
+                        l_thr[g] = l_thr[g] * alpha[g] + s[g];
+                    } else {
+                        alpha[g] = 1.0f;
+                    }
+                }
+                // the previous P V of this item must be complete before P is overwritten and O rescaled
+                if (warp == 2) FA_ACC(11);
+                if (j > 0) alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (6u << 24) | t, failed);
+                if (warp == 2) FA_ACC(12);
+                fa_fence_after();
+                {
+                    unsigned char* pcol = sP + (tid >> 6) * PHALF_BYTES + ((tid & 7) << 1);
+                    const int chunk = (tid & 63) >> 3;
+#pragma unroll
+                    for (int g = 0; g < 16; ++g)
+                        if (g < G) *reinterpret_cast<bf16*>(pcol + g * 128 + ((chunk ^ (g & 7)) << 4)) = __float2bfloat16_rn(s[g]);
+                }
+                if (j > 0 && moved) {      // the same decision in every thread: the maxima are the same
+                    float o[16];
+                    fa_tmem_ld16(tmem_base + O_COL + lane_base, o);
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) o[g] *= alpha[g];
+                    unsigned ow[16];
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) ow[g] = __float_as_uint(o[g]);
+                    fa_tmem_st16(tmem_base + O_COL + lane_base, ow);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                fa_fence_before();
+                fa_fence_async_smem();
+                __syncwarp();
+                if (lane == 0) fa_mbar_arrive(p_ready);
+                if (warp == 2) FA_ACC(13);
+            }
+            // ---------------- the item's result ----------------
+            FA_T0();
+            alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (7u << 24) | t, failed);
+            if (warp == 2) FA_ACC(14);
+            fa_fence_after();
+            float o[16];
+            fa_tmem_ld16(tmem_base + O_COL + lane_base, o);
+            fa_fence_before();
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+                if (g < G) {
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) l_thr[g] += __shfl_xor_sync(0xffffffffu, l_thr[g], off);
+                }
+            }
+            if (lane < 16) {
+                float mine = 0.0f;
+#pragma unroll
+                for (int g = 0; g < 16; ++g) mine = (lane == g) ? l_thr[g] : mine;
+                xsum[quarter * 16 + lane] = mine;
+            }
+            fd_softmax_sync();
+            if (alive) {
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    if (g < G) {
+                        const float l = (xsum[g] + xsum[16 + g]) + (xsum[32 + g] + xsum[48 + g]);
+                        const size_t row = (size_t)tok * p.nq + (size_t)w.kvh * G + g;
+                        if (w.nsplits == 1) {
+                            if (tid < D) p.out[row * D + tid] = __float2bfloat16_rn(l > 0.0f ? o[g] / l : 0.0f);
+                        } else {
+                            if (tid < D) p.part_acc[(row * p.max_splits + w.split) * D + tid] = o[g];
+                            if (tid == 0) {
+                                p.part_ml[(row * p.max_splits + w.split) * 2] = m_run[g];
+                                p.part_ml[(row * p.max_splits + w.split) * 2 + 1] = l;
+                            }
+                        }
+                    }
+                }
+            }
+            fd_softmax_sync();            // xsum is read before the next item overwrites it
+            if (warp == 2) FA_ACC(15);
+        }
+    }
+    // ---------------- common exit ----------------
+    fa_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        fa_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 fa_encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -589,8 +958,68 @@ PI_EXPORT int pi_attention_tcgen05(const void* q, int q_stride, const void* kcac
     return pi_check_launch("pi_attention_tcgen05");
 }
 
+
+PI_EXPORT int pi_attention_decode_tcgen05_supported(int page_size, int group) {
+    return (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) && group >= 1 && group <= 16;
+}
+
+// Segments of one token only (the others are skipped).  Requests whose keys are cut into more than one range
+// leave (max, sum, accumulator) per range in part_ml / part_acc for attn_merge_kernel; split_keys must be a
+// multiple of 128.
+PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
+                                          const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                                          const int* seg_start, const int* seg_len, void* out, float* part_acc, float* part_ml,
+                                          int max_splits, int split_keys, int num_segments, int nq, int nkv, int page_size,
+                                          int window, float scale, cudaStream_t stream) {
+    if (num_segments <= 0) return 0;
+    if (!(scale > 0.0f)) return pi_refuse("pi_attention_decode_tcgen05: the score scale must be positive");
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return pi_refuse("pi_attention_decode_tcgen05: nq=%d must be a positive multiple of nkv=%d", nq, nkv);
+    if (!pi_attention_decode_tcgen05_supported(page_size, nq / nkv))
+        return pi_refuse("pi_attention_decode_tcgen05: page size %d must be 8, 16, 32 or 64 and the group (%d) at most 16", page_size, nq / nkv);
+    if (split_keys <= 0 || split_keys % FA_BN != 0) return pi_refuse("pi_attention_decode_tcgen05: split_keys=%d must be a positive multiple of %d", split_keys, FA_BN);
+    if (max_splits < 1) return pi_refuse("pi_attention_decode_tcgen05: max_splits=%d must be at least 1", max_splits);
+    if (max_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return pi_refuse("pi_attention_decode_tcgen05: scratch for %d key ranges is missing", max_splits);
+    if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)kcache & 127) || ((uintptr_t)vcache & 127))
+        return pi_refuse("pi_attention_decode_tcgen05: q must be 16-byte aligned with a stride that is a multiple of 8, pages 128-byte aligned");
+    CUtensorMap mk, mv;
+    const long long rows = num_pages * nkv * page_size;
+    int rc = fa_make_map(&mk, kcache, rows, page_size);
+    if (rc) return rc;
+    rc = fa_make_map(&mv, vcache, rows, page_size);
+    if (rc) return rc;
+    const long long items = (long long)num_segments * nkv * max_splits;
+    if (items > 2147483647LL) return pi_refuse("pi_attention_decode_tcgen05: %lld items are beyond the limit", items);
+    FdParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.bt_stride = bt_stride;
+    p.seg_off = seg_off; p.seg_slot = seg_slot; p.seg_start = seg_start; p.seg_len = seg_len;
+    p.out = (bf16*)out; p.part_acc = part_acc; p.part_ml = part_ml; p.max_splits = max_splits;
+    p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.page_size = page_size; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.num_segments = num_segments; p.split_keys = split_keys; p.num_items = (int)items;
+    static int sms = 0;
+    static bool configured = false;
+    constexpr unsigned tile_bytes = (PI_HEAD_DIM / 64) * 128 * 128;
+    const size_t smem = (size_t)FD_STAGES * 2 * tile_bytes + 4 * 16 * 128 + (2 * 4 * 16 + 4 * 16) * 4 + (2 * FD_STAGES + 5) * 8 + 16 + 1024;
+    auto kernel = attn_decode_tcgen05_kernel<PI_HEAD_DIM>;
+    if (!configured) {
+        int dev = 0;
+        cudaError_t err = cudaGetDevice(&dev);
+        if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) {
+            snprintf(g_pi_error, sizeof(g_pi_error), "pi_attention_decode_tcgen05: cannot set up (%zu bytes of shared memory): %s", smem, cudaGetErrorString(err));
+            return (int)err;
+        }
+        configured = true;
+    }
+    const unsigned ctas = (unsigned)(items < sms ? items : sms);
+    pi_launch(kernel, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
+    return pi_check_launch("pi_attention_decode_tcgen05");
+}
+
 #else   // head sizes this kernel does not take
 
 PI_EXPORT int pi_attention_tcgen05_supported(int page_size) { (void)page_size; return 0; }
+PI_EXPORT int pi_attention_decode_tcgen05_supported(int page_size, int group) { (void)page_size; (void)group; return 0; }
 
 #endif

@@ -267,6 +267,15 @@ def attention_num_splits(pos: int, window: int | None, split_keys: int = SPLIT_K
 TCGEN05_ATTENTION = os.environ.get("PULSE_TCGEN05_ATTENTION", "1") != "0"
 
 
+# The persistent tcgen05 decode kernel is correct (tests run it) but not yet faster than the mma.sync decode kernel
+# (its chain per key tile is serial in one CTA per SM, where the mma.sync kernel overlaps four CTAs): off by default.
+TCGEN05_DECODE = os.environ.get("PULSE_TCGEN05_DECODE", "0") != "0"
+
+
+def attention_decode_tcgen05_usable(head_dim: int, page_size: int, group: int) -> bool:
+    return TCGEN05_ATTENTION and head_dim in (64, 128) and page_size in (8, 16, 32, 64) and 1 <= group <= 16
+
+
 def attention_tcgen05_usable(head_dim: int, page_size: int) -> bool:
     return TCGEN05_ATTENTION and head_dim in (64, 128) and page_size in (8, 16, 32, 64, 128)
 
@@ -311,7 +320,7 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
                   max_splits: int, part_acc, part_ml, nq: int, nkv: int, head_dim: int, page_size: int,
                   window: int | None, scale: float, out: torch.Tensor | None = None,
                   split_keys: int = SPLIT_KEYS, prefetch: torch.Tensor | None = None,
-                  prompt_on_tcgen05: bool = True) -> torch.Tensor:
+                  prompt_on_tcgen05: bool = True, decode_on_tcgen05: bool | None = None) -> torch.Tensor:
     """Tensor-core paged attention for bfloat16 over request segments (see csrc/attention_mma.cu)."""
     _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml)
     _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
@@ -319,6 +328,8 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
         raise KernelError("the tensor-core attention kernel takes bfloat16 only")
     if out is None:
         out = torch.empty((num_tokens, nq * head_dim), dtype=q.dtype, device=q.device)
+    if decode_on_tcgen05 is None:
+        decode_on_tcgen05 = TCGEN05_DECODE
     if has_prompt and prompt_on_tcgen05 and attention_tcgen05_usable(head_dim, page_size):
         # prompt portions on the tcgen05 kernel, single tokens (if any) on the decode kernel below
         attention_tcgen05(q, q_stride, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, num_tokens,
@@ -330,14 +341,27 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
         need = num_tokens * nq * max_splits
         if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:
             raise KernelError("scratch for the split decode attention is missing or too small")
+    decode_mode = 1 if has_decode else 0
+    if (has_decode and decode_on_tcgen05 and attention_decode_tcgen05_usable(head_dim, page_size, nq // nkv)
+            and split_keys % 128 == 0):
+        # single tokens on the persistent tcgen05 kernel; the merge of the key ranges stays with the mma library
+        tlib = _lib("attention_tcgen05", head_dim)
+        _check(tlib, tlib.pi_attention_decode_tcgen05(
+            _p(q), c_int(q_stride), _p(kcache), _p(vcache), ctypes.c_longlong(kcache.shape[0]), _p(block_table),
+            c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), _p(part_acc),
+            _p(part_ml), c_int(max_splits), c_int(split_keys), c_int(num_segments), c_int(nq), c_int(nkv),
+            c_int(page_size), c_int(window or 0), c_float(scale), _stream()), "attention_decode_tcgen05")
+        if max_splits <= 1 and not has_prompt:
+            return out
+        decode_mode = 2 if max_splits > 1 else 0
     lib = _lib("attention_mma", head_dim)
     _check(lib, lib.pi_attention_mma_prefetch(
         _p(q), c_int(q_stride), _p(kcache), _p(vcache), _p(block_table), c_int(block_table.shape[1]), _p(seg_off),
         _p(seg_slot), _p(seg_start), _p(seg_len), _p(token_seg), _p(out), _p(part_acc), _p(part_ml), c_int(max_splits),
         c_int(split_keys), c_int(num_tokens), c_int(num_segments), c_int(max_seg_len), c_int(1 if has_prompt else 0),
-        c_int(1 if has_decode else 0), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale),
+        c_int(decode_mode), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale),
         *_prefetch_args(prefetch), _stream()), "attention_mma",
-        launches=int(has_prompt) + int(has_decode) + int(has_decode and max_splits > 1))
+        launches=int(has_prompt) + int(decode_mode == 1) + int(decode_mode > 0 and max_splits > 1))
     return out
 
 

@@ -166,7 +166,7 @@ def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengt
         out = ops.attention_mma(qflat, nq * d, kv.kcache, kv.vcache, kv.table_dev, meta["seg_off"], meta["seg_slot"],
                                 meta["seg_start"], meta["seg_len"], meta["token_seg"], T, len(segs), max(lens),
                                 any(n > 1 for n in lens), any(n == 1 for n in lens), splits, acc, ml, nq, nkv, d, page,
-                                window, scale, prompt_on_tcgen05=(impl == "tcgen05"))
+                                window, scale, prompt_on_tcgen05=(impl == "tcgen05"), decode_on_tcgen05=(impl == "tcgen05"))
         if impl == "tcgen05":
             if not ops.attention_tcgen05_usable(d, page):
                 pytest.skip("the tcgen05 kernel takes head sizes 64 / 128 and page sizes 8..128")
@@ -209,10 +209,24 @@ def test_attention_bfloat16_prompt_and_decode(nq, nkv, d, page, window, impl):
     assert err < 0.03      # bfloat16 probabilities and outputs: about 2^-7 of values of order one
 
 
-@pytest.mark.parametrize("ctx", [1, 2, 15, 16, 17, 63, 64, 65, 255, 256, 257, 511, 512, 513, 1300])
-def test_attention_mma_decode_every_edge(ctx):
+@pytest.mark.parametrize("ctx", [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 512, 513, 1300])
+@pytest.mark.parametrize("impl", ["mma", "tcgen05"])
+def test_attention_decode_every_edge(ctx, impl):
     dev, ops = need_gpu(), _ops()
-    err = _attention_case(ops, dev, torch.bfloat16, "mma", 8, 2, 64, 16, None, [(0, ctx - 1, 1)], [ctx], seed=ctx)
+    err = _attention_case(ops, dev, torch.bfloat16, impl, 8, 2, 64, 16, None, [(0, ctx - 1, 1)], [ctx], seed=ctx)
+    assert err < 0.03
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (16, 1, 64, 8), (6, 3, 128, 64), (5, 5, 64, 32)])
+@pytest.mark.parametrize("window", [None, 100, 700])
+def test_attention_tcgen05_decode_many_requests(nq, nkv, d, page, window):
+    """More items than SMs would take at once, requests of very different lengths (one to several key ranges, the
+    last one partial), a prompt portion in the same step: the persistent decode kernel, its ring and the merge."""
+    dev, ops = need_gpu(), _ops()
+    lengths = [3000, 1, 257, 1025, 640, 129, 2049, 64, 513, 90, 1500, 31]
+    segs = [(i, n - 1, 1) for i, n in enumerate(lengths)]
+    segs[4] = (4, 500, 140)                                # a portion among the single tokens
+    err = _attention_case(ops, dev, torch.bfloat16, "tcgen05", nq, nkv, d, page, window, segs, lengths, seed=nq + page)
     assert err < 0.03
 
 

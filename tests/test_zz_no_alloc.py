@@ -58,7 +58,7 @@ def test_noalloc_entry_matches_regular_entry_twice():
         want = ops.attention_mma(q, nq * d, kv.kcache, kv.vcache, kv.table_dev, meta["seg_off"], meta["seg_slot"],
                                  meta["seg_start"], meta["seg_len"], meta["token_seg"], T, len(segs), max(lens),
                                  any(n > 1 for n in lens), any(n == 1 for n in lens), splits, acc, ml, nq, nkv, d, page,
-                                 window, scale, prompt_on_tcgen05=False)      # the same library as the entry under test
+                                 window, scale, prompt_on_tcgen05=False, decode_on_tcgen05=False)      # the same library as the entry under test
         got = torch.full_like(want, float("nan"))
         before = torch.cuda.memory_allocated()
         rc = _call_noalloc(lib, q, kv, meta, segs, got, splits, nq, nkv, d, page, window, scale)
