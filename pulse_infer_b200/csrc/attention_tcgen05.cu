@@ -512,14 +512,12 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 // in the layout attn_merge_kernel of attention_mma.cu combines.  Key ranges are those of the mma.sync decode
 // kernel: they depend on the request's own length only.
 // Needs a group of at most 16 query heads per kv head and pages of at most 64 keys.
-// Measured (Qwen3-8B sizes, 36 layers): 4.62 ms a step against 4.15 ms with the mma.sync decode kernel at batch 8,
-// 11.7 against 11.3 at batch 64, 10.7 against 10.5 at batch 8 and 32k context.  The cycle counters (-DFA_PROFILE)
-// show why: with ranges of 256 keys an item is two tiles, and per item the chain costs about 3,000 cycles waiting
-// for its queries, 3,500 per tile in the softmax warps (loads, shuffles for the column maxima, exchange, exponentials)
-// and 3,000 for the output - 7 us for 128 KB, where one SM's share of HBM would deliver them in under 3 us.  The
-// mma.sync kernel hides the same latencies behind four resident CTAs per SM.  The kernel is therefore not the
-// default (PULSE_TCGEN05_DECODE=1 selects it); what it needs next is two item streams per CTA and the queries of
-// the next item loaded ahead.
+// Measured (Qwen3-8B sizes, 36 layers, CUDA-graph replays, against the mma.sync decode kernel): 3.15 ms a step
+// against 3.19 at batch 1, 3.97 against 4.15 at batch 8 (context 4096), 10.2 against 11.3 at batch 64, 9.3 against
+// 10.5 at batch 8 and 32k context, 16.2 against 18.3 at batch 64 and 8k context (5.7 TB/s over weights and cache).
+// A first version (query heads padded to 16 in every loop, butterfly shuffles for the column maxima, queries
+// loaded at the start of each item) was slower than the mma.sync kernel everywhere: its cycle counters
+// (-DFA_PROFILE) showed 3,500 cycles per tile in the softmax warps and 3,000 per item waiting for the queries.
 // =============================================================================================================
 #define FD_THREADS 192
 #define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
@@ -557,22 +555,62 @@ __device__ __forceinline__ bool fd_item(const FdParams& p, int it, FdItem& w) {
     return true;
 }
 
-__device__ __forceinline__ void fa_tmem_ld16(unsigned taddr, float (&v)[16]) {
+// GP (4, 8 or 16) columns of a row of tensor memory
+template <int GP>
+__device__ __forceinline__ void fa_tmem_ld_cols(unsigned taddr, float (&v)[GP]) {
     unsigned r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
+    if constexpr (GP == 4) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+    } else if constexpr (GP == 8) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
+    } else {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+              "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr) : "memory");
+    }
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < GP; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <int GP>
+__device__ __forceinline__ void fa_tmem_st_cols(unsigned taddr, const float (&v)[GP]) {
+    if constexpr (GP == 4) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};"
+                     ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])) : "memory");
+    } else if constexpr (GP == 8) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                       "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])) : "memory");
+    } else {
+        unsigned w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(v[i]);
+        fa_tmem_st16(taddr, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fa_warp_max(float v) {      // one instruction on sm_100a
+    float m;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(m) : "f"(v));
+    return m;
 }
 __device__ __forceinline__ void fd_softmax_sync() {       // the four softmax warps
     asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-template <int D>
+// the next item of this CTA that exists, starting behind `it`
+__device__ __forceinline__ bool fd_next(const FdParams& p, int& it, FdItem& w) {
+    for (it += gridDim.x; it < p.num_items; it += gridDim.x)
+        if (fd_item(p, it, w)) return true;
+    return false;
+}
+
+// GP: the group's query heads rounded up to 4, 8 or 16
+template <int D, int GP>
 __global__ void __launch_bounds__(FD_THREADS, 1)
 attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const FdParams p) {
     constexpr int HALVES = D / 64;
@@ -580,26 +618,28 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     constexpr unsigned TILE_BYTES = HALVES * HALF_BYTES;
     constexpr unsigned STAGE_BYTES = 2 * TILE_BYTES;      // keys, then values
     constexpr unsigned QHALF_BYTES = 16 * 128;            // 16 query rows x 128 bytes
+    constexpr unsigned QBUF_BYTES = 2 * QHALF_BYTES;      // the queries of one item
     constexpr unsigned PHALF_BYTES = 16 * 128;            // 16 rows of probabilities x 64 keys
     constexpr unsigned TMEM_COLS = 64;                    // S^T twice (16 columns each), O^T (16 columns)
     constexpr unsigned O_COL = 32;
     constexpr int STAGES = FD_STAGES;
+    constexpr int QCHUNKS = (GP * (D / 8) + 127) / 128;   // 16-byte pieces of the queries per softmax thread
 
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
     unsigned char* sKV = smem;                                        // [STAGES][K tile | V tile]
-    unsigned char* sQ = sKV + STAGES * STAGE_BYTES;                   // [HALVES][16 rows][128 B]
-    unsigned char* sP = sQ + 2 * QHALF_BYTES;                         // [2 halves of keys][16 rows][128 B]
-    float* xmax = reinterpret_cast<float*>(sP + 2 * PHALF_BYTES);     // [2 parities][4 warps][16]
-    float* xsum = xmax + 2 * 4 * 16;                                  // [4 warps][16]
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(xsum + 4 * 16);
+    unsigned char* sQ = sKV + STAGES * STAGE_BYTES;                   // [2 items][HALVES][16 rows][128 B]
+    unsigned char* sP = sQ + 2 * QBUF_BYTES;                          // [2 halves of keys][16 rows][128 B]
+    float* xmax = reinterpret_cast<float*>(sP + 2 * PHALF_BYTES);     // [2 parities][16 heads][4 warps]
+    float* xsum = xmax + 2 * 16 * 4;                                  // [16 heads][4 warps]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(xsum + 16 * 4);
     unsigned long long* full = bars;                      // [STAGES] TMA -> MMA
     unsigned long long* empty = bars + STAGES;            // [STAGES] MMA -> TMA
     unsigned long long* s_full = bars + 2 * STAGES;       // [2] MMA -> softmax: scores of a tile
     unsigned long long* p_ready = s_full + 2;             // softmax (4 warps) -> MMA: P written, O rescaled, S read
     unsigned long long* pv_done = s_full + 3;             // MMA -> softmax: O updated, P free
-    unsigned long long* q_ready = s_full + 4;             // softmax (4 warps) -> MMA: the item's queries are in place
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(s_full + 5);
+    unsigned long long* q_ready = s_full + 4;             // [2] softmax (4 warps) -> MMA: an item's queries are in place
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(s_full + 6);
     volatile unsigned* failed = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -607,7 +647,8 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { fa_mbar_init(&full[i], 1); fa_mbar_init(&empty[i], 1); }
         fa_mbar_init(&s_full[0], 1); fa_mbar_init(&s_full[1], 1);
-        fa_mbar_init(p_ready, 4); fa_mbar_init(pv_done, 1); fa_mbar_init(q_ready, 4);
+        fa_mbar_init(p_ready, 4); fa_mbar_init(pv_done, 1);
+        fa_mbar_init(&q_ready[0], 4); fa_mbar_init(&q_ready[1], 4);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -617,7 +658,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     }
     // ring, queries and probabilities start as zeros: rows that nothing fills (keys past the end of a range,
     // query rows past the group) must not hold NaN bit patterns
-    for (unsigned i = threadIdx.x; i < (STAGES * STAGE_BYTES + 2 * QHALF_BYTES + 2 * PHALF_BYTES) / 16; i += FD_THREADS)
+    for (unsigned i = threadIdx.x; i < (STAGES * STAGE_BYTES + 2 * QBUF_BYTES + 2 * PHALF_BYTES) / 16; i += FD_THREADS)
         reinterpret_cast<uint4*>(sKV)[i] = make_uint4(0, 0, 0, 0);
     pdl_wait();
     fa_fence_async_smem();
@@ -630,11 +671,10 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         // ---------------- TMA producer: lane = page of the key tile; runs ahead across items ----------------
         const int ps = p.page_size, pages_per_tile = FA_BN / ps;
         const unsigned page_bytes = (unsigned)ps * 128u;
-        int t = 0;
+        int t = 0, it = (int)blockIdx.x - (int)gridDim.x;
+        FdItem w;
         bool ok = true;
-        for (int it = blockIdx.x; it < p.num_items && ok && !*failed; it += gridDim.x) {
-            FdItem w;
-            if (!fd_item(p, it, w)) continue;
+        while (ok && !*failed && fd_next(p, it, w)) {
             const int* table = p.block_table + (size_t)p.seg_slot[w.seg] * p.bt_stride;
             for (int j = 0; j < w.ntiles; ++j, ++t) {
                 const int st = t % STAGES, use = t / STAGES;
@@ -664,34 +704,35 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             // S^T: M 128 keys x N 16 heads, both K-major.  O^T: M 128 (head dimension) x N 16, A (values) MN-major.
             const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             const unsigned idesc_pv = idesc_s | (1u << 15);
-            int t = 0, ic = 0;
+            int t = 0, ic = 0, it = (int)blockIdx.x - (int)gridDim.x;
+            FdItem w;
             bool ok = true;
-            auto issue_s = [&](int tt) -> bool {        // scores of tile tt into buffer tt & 1
+            auto issue_s = [&](int tt, int qbuf) -> bool {        // scores of tile tt into buffer tt & 1
                 const int st = tt % STAGES;
                 FA_T0();
                 if (!fa_mbar_wait(&full[st], (tt / STAGES) & 1, (2u << 24) | tt, failed)) return false;
                 FA_ACC(3);
                 fa_fence_after();
                 const unsigned char* kt = sKV + st * STAGE_BYTES;
+                const unsigned char* qt = sQ + qbuf * QBUF_BYTES;
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         fa_mma(tmem_base + (tt & 1) * 16, fa_desc_kmajor(fa_smem(kt + h * HALF_BYTES) + k * 32),
-                               fa_desc_kmajor(fa_smem(sQ + h * QHALF_BYTES) + k * 32), idesc_s, (h > 0 || k > 0) ? 1u : 0u);
+                               fa_desc_kmajor(fa_smem(qt + h * QHALF_BYTES) + k * 32), idesc_s, (h > 0 || k > 0) ? 1u : 0u);
                 fa_commit(&s_full[tt & 1]);
                 return true;
             };
-            for (int it = blockIdx.x; it < p.num_items && ok && !*failed; it += gridDim.x) {
-                FdItem w;
-                if (!fd_item(p, it, w)) continue;
+            while (ok && !*failed && fd_next(p, it, w)) {
                 FA_T0();
-                if (!fa_mbar_wait(q_ready, ic & 1, (3u << 24) | ic, failed)) break;
+                if (!fa_mbar_wait(&q_ready[ic & 1], (ic >> 1) & 1, (3u << 24) | ic, failed)) break;
                 FA_ACC(4);
+                const int qbuf = ic & 1;
                 ++ic;
-                ok = issue_s(t);
+                ok = issue_s(t, qbuf);
                 for (int j = 0; j < w.ntiles && ok; ++j, ++t) {
-                    if (j + 1 < w.ntiles) ok = issue_s(t + 1);      // the next scores while this tile is in its softmax
+                    if (j + 1 < w.ntiles) ok = issue_s(t + 1, qbuf);      // the next scores while this tile is in its softmax
                     if (!ok) break;
                     FA_T0();
                     if (!fa_mbar_wait(p_ready, t & 1, (4u << 24) | t, failed)) { ok = false; break; }
@@ -715,74 +756,77 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         const unsigned lane_base = (unsigned)(quarter * 32) << 16;
         int t = 0, ic = 0;
         bool alive = true;
-        for (int it = blockIdx.x; it < p.num_items; it += gridDim.x) {
-            FdItem w;
-            if (!fd_item(p, it, w)) continue;
-            // the item's queries: rows g < G of a [16, D] K-major tile (the previous item's products are complete)
+        // the queries of an item: rows g < G of a [16, D] K-major tile; fetched into registers early, stored later
+        uint4 qv[QCHUNKS];
+        auto fetch_q = [&](const FdItem& w) {
             const int tok = p.seg_off[w.seg];
-            for (int idx = tid; idx < G * (D / 8); idx += 128) {
-                const int g = idx / (D / 8), c = idx % (D / 8);
-                const uint4 v = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.q_stride + (size_t)(w.kvh * G + g) * D + c * 8);
-                *reinterpret_cast<uint4*>(sQ + (c / 8) * QHALF_BYTES + g * 128 + (((c % 8) ^ (g & 7)) << 4)) = v;
+#pragma unroll
+            for (int c = 0; c < QCHUNKS; ++c) {
+                const int idx = tid + c * 128;
+                qv[c] = make_uint4(0, 0, 0, 0);
+                if (idx < G * (D / 8))
+                    qv[c] = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.q_stride + (size_t)(w.kvh * G + idx / (D / 8)) * D + (idx % (D / 8)) * 8);
+            }
+        };
+        auto store_q = [&](int buf) {
+#pragma unroll
+            for (int c = 0; c < QCHUNKS; ++c) {
+                const int idx = tid + c * 128;
+                if (idx < G * (D / 8)) {
+                    const int g = idx / (D / 8), ch = idx % (D / 8);
+                    *reinterpret_cast<uint4*>(sQ + buf * QBUF_BYTES + (ch / 8) * QHALF_BYTES + g * 128 + (((ch % 8) ^ (g & 7)) << 4)) = qv[c];
+                }
             }
             fa_fence_async_smem();
             __syncwarp();
-            if (lane == 0) fa_mbar_arrive(q_ready);
-            ++ic;
-            float m_run[16], l_thr[16];
+            if (lane == 0) fa_mbar_arrive(&q_ready[buf]);
+        };
+        FdItem w, wn;
+        int it = (int)blockIdx.x - (int)gridDim.x;
+        bool have = fd_next(p, it, w);
+        if (have) { fetch_q(w); store_q(0); }
+        while (have) {
+            int it_next = it;
+            const bool have_next = fd_next(p, it_next, wn);
+            if (have_next) fetch_q(wn);                    // lands while this item's first tile is worked on
+            const int tok = p.seg_off[w.seg];
+            float m_run[GP], l_thr[GP];
 #pragma unroll
-            for (int g = 0; g < 16; ++g) { m_run[g] = -INFINITY; l_thr[g] = 0.0f; }
+            for (int g = 0; g < GP; ++g) { m_run[g] = -INFINITY; l_thr[g] = 0.0f; }
             for (int j = 0; j < w.ntiles; ++j, ++t) {
                 FA_T0();
                 alive = alive && fa_mbar_wait(&s_full[t & 1], (t >> 1) & 1, (5u << 24) | t, failed);
                 if (warp == 2) FA_ACC(8);
                 fa_fence_after();
-                float s[16];
-                fa_tmem_ld16(tmem_base + (t & 1) * 16 + lane_base, s);
+                float s[GP];
+                fa_tmem_ld_cols<GP>(tmem_base + (t & 1) * 16 + lane_base, s);
                 const int key = w.kb + j * FA_BN + tid;
                 const bool vis = key <= w.pos && key >= w.lo && key < w.ke;
-                float wm[16];
-#pragma unroll
-                for (int g = 0; g < 16; ++g) {
-                    s[g] = vis ? s[g] * p.scale_log2 : -INFINITY;
-                    wm[g] = s[g];
-                }
-#pragma unroll
-                for (int g = 0; g < 16; ++g) {
-                    if (g < G) {
-#pragma unroll
-                        for (int off = 16; off > 0; off >>= 1) wm[g] = fmaxf(wm[g], __shfl_xor_sync(0xffffffffu, wm[g], off));
-                    }
-                }
                 float* xm = xmax + (t & 1) * 64;
-                if (lane < 16) {
-                    float mine = -INFINITY;
 #pragma unroll
-                    for (int g = 0; g < 16; ++g) mine = (lane == g) ? wm[g] : mine;
-                    xm[quarter * 16 + lane] = mine;
+                for (int g = 0; g < GP; ++g) {
+                    s[g] = vis ? s[g] * p.scale_log2 : -INFINITY;
+                    const float wm = fa_warp_max(s[g]);
+                    if (lane == 0) xm[g * 4 + quarter] = wm;
                 }
                 if (warp == 2) FA_ACC(9);
                 fd_softmax_sync();
                 if (warp == 2) FA_ACC(10);
-                float alpha[16];
+                float alpha[GP];
                 bool moved = false;
 #pragma unroll
-                for (int g = 0; g < 16; ++g) {
-                    if (g < G) {
-                        const float mt = fmaxf(fmaxf(xm[g], xm[16 + g]), fmaxf(xm[32 + g], xm[48 + g]));
-                        const float m_new = fmaxf(m_run[g], mt);
-                        const float base = (m_new == -INFINITY) ? 0.0f : m_new;
-                        alpha[g] = fa_ex2(m_run[g] - base);
-                        moved = moved || (alpha[g] != 1.0f);
-                        m_run[g] = m_new;
-                        s[g] = fa_ex2(s[g] - base);                 // -inf gives 0
-                        l_thr[g] = l_thr[g] * alpha[g] + s[g];
-                    } else {
-                        alpha[g] = 1.0f;
-                    }
+                for (int g = 0; g < GP; ++g) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(xm + g * 4);
+                    const float m_new = fmaxf(m_run[g], fmaxf(fmaxf(q4.x, q4.y), fmaxf(q4.z, q4.w)));
+                    const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+                    alpha[g] = fa_ex2(m_run[g] - base);
+                    moved = moved || (alpha[g] != 1.0f);
+                    m_run[g] = m_new;
+                    s[g] = fa_ex2(s[g] - base);                 // -inf gives 0
+                    l_thr[g] = l_thr[g] * alpha[g] + s[g];
                 }
-                // the previous P V of this item must be complete before P is overwritten and O rescaled
                 if (warp == 2) FA_ACC(11);
+                // the previous P V of this item must be complete before P is overwritten and O rescaled
                 if (j > 0) alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (6u << 24) | t, failed);
                 if (warp == 2) FA_ACC(12);
                 fa_fence_after();
@@ -790,24 +834,21 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     unsigned char* pcol = sP + (tid >> 6) * PHALF_BYTES + ((tid & 7) << 1);
                     const int chunk = (tid & 63) >> 3;
 #pragma unroll
-                    for (int g = 0; g < 16; ++g)
+                    for (int g = 0; g < GP; ++g)
                         if (g < G) *reinterpret_cast<bf16*>(pcol + g * 128 + ((chunk ^ (g & 7)) << 4)) = __float2bfloat16_rn(s[g]);
                 }
                 if (j > 0 && moved) {      // the same decision in every thread: the maxima are the same
-                    float o[16];
-                    fa_tmem_ld16(tmem_base + O_COL + lane_base, o);
+                    float o[GP];
+                    fa_tmem_ld_cols<GP>(tmem_base + O_COL + lane_base, o);
 #pragma unroll
-                    for (int g = 0; g < 16; ++g) o[g] *= alpha[g];
-                    unsigned ow[16];
-#pragma unroll
-                    for (int g = 0; g < 16; ++g) ow[g] = __float_as_uint(o[g]);
-                    fa_tmem_st16(tmem_base + O_COL + lane_base, ow);
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    for (int g = 0; g < GP; ++g) o[g] *= alpha[g];
+                    fa_tmem_st_cols<GP>(tmem_base + O_COL + lane_base, o);
                 }
                 fa_fence_before();
                 fa_fence_async_smem();
                 __syncwarp();
                 if (lane == 0) fa_mbar_arrive(p_ready);
+                if (j == 0 && have_next) store_q((ic + 1) & 1);     // the next item's queries, fetched above
                 if (warp == 2) FA_ACC(13);
             }
             // ---------------- the item's result ----------------
@@ -815,28 +856,22 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (7u << 24) | t, failed);
             if (warp == 2) FA_ACC(14);
             fa_fence_after();
-            float o[16];
-            fa_tmem_ld16(tmem_base + O_COL + lane_base, o);
+            float o[GP];
+            fa_tmem_ld_cols<GP>(tmem_base + O_COL + lane_base, o);
             fa_fence_before();
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {
-                if (g < G) {
+            for (int g = 0; g < GP; ++g) {
 #pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) l_thr[g] += __shfl_xor_sync(0xffffffffu, l_thr[g], off);
-                }
-            }
-            if (lane < 16) {
-                float mine = 0.0f;
-#pragma unroll
-                for (int g = 0; g < 16; ++g) mine = (lane == g) ? l_thr[g] : mine;
-                xsum[quarter * 16 + lane] = mine;
+                for (int off = 16; off > 0; off >>= 1) l_thr[g] += __shfl_xor_sync(0xffffffffu, l_thr[g], off);
+                if (lane == 0) xsum[g * 4 + quarter] = l_thr[g];
             }
             fd_softmax_sync();
             if (alive) {
 #pragma unroll
-                for (int g = 0; g < 16; ++g) {
+                for (int g = 0; g < GP; ++g) {
                     if (g < G) {
-                        const float l = (xsum[g] + xsum[16 + g]) + (xsum[32 + g] + xsum[48 + g]);
+                        const float4 q4 = *reinterpret_cast<const float4*>(xsum + g * 4);
+                        const float l = (q4.x + q4.y) + (q4.z + q4.w);
                         const size_t row = (size_t)tok * p.nq + (size_t)w.kvh * G + g;
                         if (w.nsplits == 1) {
                             if (tid < D) p.out[row * D + tid] = __float2bfloat16_rn(l > 0.0f ? o[g] / l : 0.0f);
@@ -852,6 +887,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             }
             fd_softmax_sync();            // xsum is read before the next item overwrites it
             if (warp == 2) FA_ACC(15);
+            w = wn; have = have_next; it = it_next; ++ic;
         }
     }
     // ---------------- common exit ----------------
@@ -999,13 +1035,14 @@ PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const voi
     static int sms = 0;
     static bool configured = false;
     constexpr unsigned tile_bytes = (PI_HEAD_DIM / 64) * 128 * 128;
-    const size_t smem = (size_t)FD_STAGES * 2 * tile_bytes + 4 * 16 * 128 + (2 * 4 * 16 + 4 * 16) * 4 + (2 * FD_STAGES + 5) * 8 + 16 + 1024;
-    auto kernel = attn_decode_tcgen05_kernel<PI_HEAD_DIM>;
+    const size_t smem = (size_t)FD_STAGES * 2 * tile_bytes + 6 * 16 * 128 + (2 * 4 * 16 + 4 * 16) * 4 + (2 * FD_STAGES + 6) * 8 + 16 + 1024;
     if (!configured) {
         int dev = 0;
         cudaError_t err = cudaGetDevice(&dev);
         if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (err == cudaSuccess) err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) {
             snprintf(g_pi_error, sizeof(g_pi_error), "pi_attention_decode_tcgen05: cannot set up (%zu bytes of shared memory): %s", smem, cudaGetErrorString(err));
             return (int)err;
@@ -1013,7 +1050,9 @@ PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const voi
         configured = true;
     }
     const unsigned ctas = (unsigned)(items < sms ? items : sms);
-    pi_launch(kernel, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
+    if (p.group <= 4) pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 4>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
+    else if (p.group <= 8) pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 8>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
+    else pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 16>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
     return pi_check_launch("pi_attention_decode_tcgen05");
 }
 

@@ -176,7 +176,7 @@ class StepContext:
                 sc = AttentionScratch(1, None, None)
             else:
                 num_decode = sum(1 for s in self.segments if len(s.tokens) == 1)
-                split_keys = self.split_keys or ops.choose_split_keys(num_decode, num_kv_heads, self.decode_pos_max)
+                split_keys = self.split_keys or ops.choose_split_keys(num_decode, num_kv_heads, self.decode_pos_max, head_dim)
                 splits = self.splits_bound or ops.attention_num_splits(self.decode_pos_max, window, split_keys)
                 if splits > 1:
                     rows = self.num_tokens * num_heads

@@ -88,7 +88,8 @@ class DecodeGraphs:
         specs = [cs for cs in self.runner.model.cache_specs() if cs is not None]
         windows = {cs.window for cs in specs}
         pos_max = max(s.start for s in segments)
-        split_keys = ops.choose_split_keys(len(segments), max((cs.num_kv_heads for cs in specs), default=1), pos_max)
+        split_keys = ops.choose_split_keys(len(segments), max((cs.num_kv_heads for cs in specs), default=1), pos_max,
+                                           specs[0].head_dim if specs else None)
         need = max(ops.attention_num_splits(pos_max, w, split_keys) for w in windows) if windows else 1
         key = (len(segments), split_keys, _pow2_at_least(need))
         g = self.graphs.get(key)

@@ -238,12 +238,20 @@ def attention_simple(q: torch.Tensor, q_stride: int, kcache, vcache, block_table
     return out
 
 
-def choose_split_keys(num_decode: int, num_kv_heads: int, max_pos: int) -> int:
-    """Keys per range of the split decode attention.  Short ranges give a small batch enough CTAs to
-    fill the GPU; a large batch has enough already and prefers long ranges (less start-up cost per byte)."""
+def choose_split_keys(num_decode: int, num_kv_heads: int, max_pos: int, head_dim: int | None = None) -> int:
+    """Keys per range of the split decode attention (from measurements on B200).
+    The persistent tcgen05 kernel (head sizes 64 / 128) wants about one item per SM and as few ranges as that
+    allows: the longest range that still gives 120 items.  The mma.sync kernel wants several CTAs per SM: short
+    ranges for a small batch, long ones (less start-up cost per byte) for a large one."""
     forced = os.environ.get("PULSE_SPLIT_KEYS")
     if forced:
         return int(forced)
+    if TCGEN05_DECODE and TCGEN05_ATTENTION and head_dim in (64, 128):
+        pairs = num_decode * max(num_kv_heads, 1)
+        for keys in (2048, 1024, 512):
+            if pairs * (max_pos + 1) >= 120 * keys:
+                return keys
+        return SPLIT_KEYS
     tiles = (max_pos + 256) // 256
     ctas = num_decode * max(num_kv_heads, 1) * tiles
     if ctas > 48 * 148:
@@ -267,9 +275,7 @@ def attention_num_splits(pos: int, window: int | None, split_keys: int = SPLIT_K
 TCGEN05_ATTENTION = os.environ.get("PULSE_TCGEN05_ATTENTION", "1") != "0"
 
 
-# The persistent tcgen05 decode kernel is correct (tests run it) but not yet faster than the mma.sync decode kernel
-# (its chain per key tile is serial in one CTA per SM, where the mma.sync kernel overlaps four CTAs): off by default.
-TCGEN05_DECODE = os.environ.get("PULSE_TCGEN05_DECODE", "0") != "0"
+TCGEN05_DECODE = os.environ.get("PULSE_TCGEN05_DECODE", "1") != "0"     # single tokens on the persistent tcgen05 kernel
 
 
 def attention_decode_tcgen05_usable(head_dim: int, page_size: int, group: int) -> bool:
