@@ -518,6 +518,10 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 // A first version (query heads padded to 16 in every loop, butterfly shuffles for the column maxima, queries
 // loaded at the start of each item) was slower than the mma.sync kernel everywhere: its cycle counters
 // (-DFA_PROFILE) showed 3,500 cycles per tile in the softmax warps and 3,000 per item waiting for the queries.
+// Two further variants were measured in the same run and dropped: filling the rows of a partial tile from a spare
+// page instead of zeroing the ring at the start (4.04 against 4.00 ms at batch 8, 10.51 against 10.19 at batch 64),
+// and the sums of the probabilities by a product with a tile of ones instead of a reduction across threads at
+// the end of an item (no difference, and shorter key ranges were no faster with it).
 // =============================================================================================================
 #define FD_THREADS 192
 #define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
