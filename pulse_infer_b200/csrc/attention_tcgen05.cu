@@ -291,10 +291,9 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    pdl_wait();   // q and the pages are written by the kernels before this one
-
     // the ring starts as zeros: rows of a value tile that no page fills must not hold NaN bit patterns (0 x NaN)
     for (unsigned i = threadIdx.x; i < FA_STAGES * TILE_BYTES / 16; i += FA_THREADS) reinterpret_cast<uint4*>(sKV)[i] = make_uint4(0, 0, 0, 0);
+    pdl_wait();   // q and the pages are written by the kernels before this one; all above touched this CTA only
     // Q: thread r of the softmax warps copies row r into the swizzled K-major layout (16-byte chunk c of a
     // 128-byte row goes to chunk c ^ (row & 7))
     if (warp >= 2) {
