@@ -314,7 +314,8 @@ def run_ours(args) -> dict:
                    "peaks": peak_source},
         "clocks": clock_info,
         "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": h2d_e, "d2h_bytes_per_step": d2h_e},
+                "h2d_bytes_per_step": h2d_e, "d2h_bytes_per_step": d2h_e,
+                "note": "Engine.step() with lookahead: each call launches a step and reads the ids of the step before"},
         "gpu_launches": launches,
         "prefill": {"value": round(PROMPT * 1000.0 / prefill_ms, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
                     "frac": round(pf / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},

@@ -20,10 +20,13 @@ class Engine:
                  device: str = "cuda:0", page_size: int = 16, num_pages: int | None = None,
                  max_tokens: int | None = None, max_batch_size: int = 8, chunk_size: int = 256,
                  max_tokens_per_step: int | None = None, max_tokens_per_request: int | None = None,
-                 use_cuda_graphs: bool = True, attention_impl: str = "auto", rope_pairing: str | None = None):
+                 use_cuda_graphs: bool = True, attention_impl: str = "auto", rope_pairing: str | None = None,
+                 lookahead: bool | None = None):
         """``model``: folder with config.json and safetensors; or ``config`` + ``seed`` for random weights.
         The page pool is ``num_pages`` pages of ``page_size`` tokens, or enough for ``max_tokens`` tokens
-        (default: ``max_batch_size`` requests of the model's longest context, capped at 1M tokens)."""
+        (default: ``max_batch_size`` requests of the model's longest context, capped at 1M tokens).
+        ``lookahead`` (default: on with CUDA graphs): a decode step stays in flight when ``step()`` returns and its
+        tokens are read while the next one runs; ``step()`` then returns the tokens of the step before."""
         spec_options = {} if rope_pairing is None else {"rope_pairing": rope_pairing}
         if num_pages is None and max_tokens is None:
             from .config.registry import load_config
@@ -38,7 +41,8 @@ class Engine:
         self.sampler = Sampler(self.runner.runtime.device)
         self.engine = ContinuousBatchEngine(self.runner, self.sampler, getattr(self.config, "eos_token_ids", ()),
                                             max_batch_size=max_batch_size, chunk_size=chunk_size,
-                                            max_tokens_per_step=max_tokens_per_step)
+                                            max_tokens_per_step=max_tokens_per_step,
+                                            lookahead=use_cuda_graphs if lookahead is None else lookahead)
 
     # ---- the reference engine's calls ------------------------------------------------------------------
     def add_request(self, prompt_tokens, max_new_tokens: int = 32, *, temperature: float = 0.0, top_k: int = 0,

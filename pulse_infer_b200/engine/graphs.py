@@ -55,8 +55,12 @@ class DecodeGraph:
         self.copied[i].record()
         self.ctx._bind(segments, lay, T, R, W)
 
-    def run(self, segments) -> torch.Tensor:
+    def run(self, segments, tokens_from=None) -> torch.Tensor:
         self._refill(segments)
+        if tokens_from is not None:      # ids sampled by the step before, still on the device
+            if tokens_from.dtype != torch.int32 or tokens_from.numel() != self.num_requests:
+                raise ValueError("tokens_from must hold one int32 id per request of the step")
+            self.ctx.tokens.copy_(tokens_from.reshape(-1))
         if self.graph is None:
             model = self.runner.model
             # once eagerly (library initialisation, kernel attributes), then capture the same work
@@ -84,7 +88,7 @@ class DecodeGraphs:
     def eligible(self, segments) -> bool:
         return all(len(s.tokens) == 1 and list(s.want) == [0] for s in segments)
 
-    def run(self, segments) -> torch.Tensor:
+    def run(self, segments, tokens_from=None) -> torch.Tensor:
         specs = [cs for cs in self.runner.model.cache_specs() if cs is not None]
         windows = {cs.window for cs in specs}
         pos_max = max(s.start for s in segments)
@@ -98,4 +102,4 @@ class DecodeGraphs:
                 self.graphs.pop(next(iter(self.graphs)))
             g = DecodeGraph(self.runner, *key)
             self.graphs[key] = g
-        return g.run(segments)
+        return g.run(segments, tokens_from)

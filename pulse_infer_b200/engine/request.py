@@ -34,6 +34,7 @@ class InferenceRequest:
     num_computed_tokens: int = 0
     finish_reason: str | None = None
     num_preemptions: int = 0
+    unresolved: int = 0          # trailing entries of generated_tokens that were sampled but not read back yet
     arrival_time: float = field(default_factory=time.monotonic)
     start_time: float | None = None
     finish_time: float | None = None
@@ -61,6 +62,8 @@ class InferenceRequest:
         return generated == 0 or len(self.prompt_tokens) + generated - self.num_computed_tokens > 1
 
     def has_pending_input(self) -> bool:
+        if self.unresolved and self.num_generated() >= self.max_new_tokens:
+            return False       # the token still on the device is the last one allowed: it will not be fed
         return not self.is_finished() and self.num_computed_tokens < self.total_input_tokens()
 
     def can_generate_more(self) -> bool:
@@ -116,10 +119,36 @@ class InferenceRequest:
         if self.is_finished():
             return False
         self.generated_tokens.append(token)
+        return self._after_token(token, eos_token_ids)
+
+    def _after_token(self, token: int, eos_token_ids) -> bool:
         if token == -1:
             self.finish("invalid_token")
         elif not self.ignore_eos and token in eos_token_ids:
             self.finish("eos")
-        elif self.num_generated() >= self.max_new_tokens:
+        elif self.num_generated() - self.unresolved >= self.max_new_tokens:
             self.finish("length")
         return not self.is_finished()
+
+    # A token that was sampled on the device and is read back a step later: a place is kept for it at once, so
+    # that the scheduler can plan the next step, and filled when the value arrives (oldest place first).
+    PENDING_TOKEN = 0
+
+    def add_pending_token(self) -> None:
+        self.generated_tokens.append(self.PENDING_TOKEN)
+        self.unresolved += 1
+
+    def resolve_pending_token(self, token: int, eos_token_ids) -> bool:
+        """Fill the oldest kept place; returns False when the request finished with this token."""
+        self.generated_tokens[len(self.generated_tokens) - self.unresolved] = token
+        self.unresolved -= 1
+        return self._after_token(token, eos_token_ids)
+
+    def drop_pending_tokens(self) -> None:
+        """Places kept for tokens sampled after the one that ended the request."""
+        while self.unresolved > 0:
+            self.generated_tokens.pop()
+            self.unresolved -= 1
+
+    def resolved_tokens(self) -> list:
+        return self.generated_tokens[:len(self.generated_tokens) - self.unresolved]

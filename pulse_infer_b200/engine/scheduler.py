@@ -200,8 +200,9 @@ class ContinuousBatchScheduler:
             self.stats_prefill_tokens += want
             budget -= want
 
-        # a step must make progress: if requests run but nothing was planned, the newest one gives way
-        if not batch.entries and self.running_requests:
+        # a step must make progress: if requests run but nothing was planned, the newest one gives way (unless the
+        # running requests only wait for sampled tokens to be read back)
+        if not batch.entries and self.running_requests and not any(r.unresolved for r in self.running_requests):
             victim = self.running_requests[-1]
             if len(self.running_requests) == 1:
                 self.cache.close(victim.request_id)

@@ -75,13 +75,21 @@ class ModelRunner:
         for s in segments:
             self.cache.reserve(s.request_id, s.start + len(s.tokens))
 
-    def step(self, segments: list) -> torch.Tensor:
+    def takes_device_tokens(self, segments: list) -> bool:
+        """Whether ``step(segments, tokens_from=...)`` is possible: a captured step of single tokens."""
+        return self.graphs is not None and self.graphs.eligible(segments)
+
+    def step(self, segments: list, tokens_from: torch.Tensor | None = None) -> torch.Tensor:
         """segments: list of ``Segment(request_id, tokens, want)``.  Returns float32 logits
-        [number of wanted places, vocab] in the order of the segments and of their ``want`` lists."""
+        [number of wanted places, vocab] in the order of the segments and of their ``want`` lists.
+        ``tokens_from`` (int32 on the device, one id per segment, captured steps only): the input tokens are taken
+        from there instead of from the segments - the ids the previous step sampled, not yet read by the host."""
         self.prepare(segments)
         self.cache.sync_tables()
+        if tokens_from is not None and not self.takes_device_tokens(segments):
+            raise StepError("tokens can come from the device only in a captured step of single tokens")
         if self.graphs is not None and self.graphs.eligible(segments):
-            logits = self.graphs.run(segments)      # valid until the next captured step runs
+            logits = self.graphs.run(segments, tokens_from)      # valid until the next captured step runs
             ctx = None
         else:
             ctx = StepContext.build(segments, self.runtime, self.cache)

@@ -23,9 +23,15 @@ class Sampler:
     def sample(self, logits: torch.Tensor, params: list, draw_index: list, history: list | None = None) -> list:
         """logits float32 [n, V]; params[i] SamplingParams; draw_index[i] how many tokens request i has
         drawn so far; history[i] the tokens a presence penalty looks at.  Returns n token ids."""
+        out = self.sample_device(logits, params, draw_index, history)
+        return [] if out is None else out.tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: list, draw_index: list, history: list | None = None):
+        """The same, but the token ids stay on the device (int32 [n], or None for no rows): the caller reads them
+        when it needs them, and the next step can take them as its input without a round trip."""
         n = logits.shape[0]
         if n == 0:
-            return []
+            return None
         if any(p.edits_logits for p in params):
             logits = logits.clone()
             rows, toks, vals_add, rows_set, toks_set = [], [], [], [], []
@@ -42,7 +48,7 @@ class Sampler:
                 ops.logit_edit(logits, mk(rows_set, torch.int32), mk(toks_set, torch.int32),
                                mk([float("-inf")] * len(rows_set), torch.float32), True)
         if all(p.greedy for p in params):
-            return ops.argmax(logits).tolist()
+            return ops.argmax(logits)
         mk = lambda v, dt: torch.tensor(v, dtype=dt, device=self.device)  # noqa: E731
         out = ops.sample(
             logits,
@@ -51,7 +57,7 @@ class Sampler:
             mk([p.top_p for p in params], torch.float32),
             mk([_as_i64(p.seed) for p in params], torch.int64),
             mk(list(draw_index), torch.int64))
-        return out.tolist()
+        return out
 
 
 def _as_i64(v: int) -> int:

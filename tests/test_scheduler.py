@@ -222,3 +222,97 @@ def test_random_workloads_match_an_unconstrained_run(seed):
     for rid, (p, m) in zip(ids, reqs):
         assert engine.get_result(rid) == expected_output(p, m), f"request {rid}"
     assert cache.free_pages() == [cache.num_pages] and cache.num_free_slots == 8
+
+
+# ---- lookahead: a step of single tokens stays in flight, its ids are read a step later -----------------------------
+class LookaheadRunner(ModelRunner):
+    """The stand-in's version of a captured step that takes its input ids from the device: the ids of the step
+    before arrive as a tensor and replace the places kept in the segments."""
+
+    def takes_device_tokens(self, segments):
+        return all(len(s.tokens) == 1 and list(s.want) == [0] for s in segments)
+
+    def step(self, segments, tokens_from=None):
+        if tokens_from is not None:
+            assert self.takes_device_tokens(segments) and tokens_from.numel() == len(segments)
+            for s, t in zip(segments, tokens_from.tolist()):
+                s.tokens = [int(t)]
+        return super().step(segments)
+
+
+class DeviceArgmaxSampler(ArgmaxSampler):
+    reads = 0
+
+    def sample_device(self, logits, params, draw_index, history=None):
+        return logits.argmax(-1).to(torch.int32)
+
+
+def make_lookahead_engine(num_pages=64, page_size=4, max_batch_size=4, chunk_size=8, max_tokens_per_step=None, eos=()):
+    cache = CacheManager([CacheSpec(1, 16, None)], [None], page_size, num_pages, 8, 256, allocate_pools=False)
+    model = StandInModel()
+    runner = LookaheadRunner(model, cache, Runtime(torch.device("cpu"), "float32"))
+    engine = ContinuousBatchEngine(runner, DeviceArgmaxSampler(), eos, max_batch_size=max_batch_size, chunk_size=chunk_size,
+                                   max_tokens_per_step=max_tokens_per_step, lookahead=True)
+    return engine, model, cache
+
+
+def test_lookahead_keeps_a_decode_step_in_flight_and_returns_its_tokens_a_step_later():
+    prompt = [3, 1, 4, 1, 5]
+    want = expected_output(prompt, 5)
+    engine, model, cache = make_lookahead_engine(chunk_size=16)
+    rid = engine.add_request(prompt, 5)
+    assert engine.step() == [(rid, want[0])]          # the prompt step samples; it is not a step of single tokens
+    assert engine.step() == []                        # first decode step: launched, its token stays on the device
+    assert engine.get_result(rid) == want[:1] and engine.get_request(rid).unresolved == 1
+    assert engine.step() == [(rid, want[1])]          # second decode step launched on the device token; first one read
+    assert [s for s in model.steps[-1]] == [(rid, 6, 1)] and model.history[rid][-1] == want[1]
+    outs = []
+    while engine.has_work():
+        outs += engine.step()
+    assert [t for _, t in outs] == want[2:] and engine.get_result(rid) == want
+    assert engine.get_request(rid).finish_reason == "length" and engine.get_request(rid).unresolved == 0
+    assert cache.free_pages() == [64]
+    # the last allowed token is not fed back: 5 prompt tokens + 4 fed samples
+    assert len(model.history[rid]) == 9
+
+
+def test_lookahead_eos_read_late_drops_the_extra_token():
+    prompt = [2, 7, 1, 8, 2, 8]
+    free_run = expected_output(prompt, 12)
+    eos = (free_run[4],)
+    want = expected_output(prompt, 12, eos)
+    assert len(want) == 5
+    engine, model, cache = make_lookahead_engine(chunk_size=16, eos=eos)
+    rid = engine.add_request(prompt, 12)
+    engine.run_until_complete()
+    assert engine.get_result(rid) == want and engine.get_request(rid).finish_reason == "eos"
+    assert engine.get_request(rid).generated_tokens == want and cache.free_pages() == [64]
+    assert len(model.history[rid]) == len(prompt) + len(want)        # one step ran past the end; its token is dropped
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_lookahead_random_workloads_match_an_unconstrained_run(seed):
+    """Admissions, portions, preemptions, EOS and length limits while steps are in flight: the results are those of
+    the plain loop."""
+    rng = np.random.RandomState(100 + seed)
+    reqs = [([int(t) for t in rng.randint(1, VOCAB, size=rng.randint(1, 40))], int(rng.randint(1, 25)))
+            for _ in range(12)]
+    eos = tuple(int(t) for t in rng.randint(1, VOCAB, size=3)) if seed % 2 else ()
+    engine, model, cache = make_lookahead_engine(num_pages=int(rng.randint(17, 30)), page_size=4, max_batch_size=4,
+                                                 chunk_size=int(rng.choice([3, 8, 32])),
+                                                 max_tokens_per_step=int(rng.choice([6, 16, 64])), eos=eos)
+    ids, seen = [], {}
+    pending = list(reqs)
+    while pending or engine.has_work():
+        while pending and rng.rand() < 0.5:
+            p, m = pending.pop(0)
+            ids.append(engine.add_request(p, m))
+        if engine.has_work():
+            for rid, tok in engine.step():
+                seen.setdefault(rid, []).append(tok)
+            cache.check_invariants()
+    for rid, (p, m) in zip(ids, reqs):
+        assert engine.get_result(rid) == expected_output(p, m, eos), f"request {rid}"
+        assert seen.get(rid, []) == engine.get_result(rid)             # every token was handed out once, in order
+        assert engine.get_request(rid).unresolved == 0
+    assert cache.free_pages() == [cache.num_pages] and cache.num_free_slots == 8
