@@ -327,7 +327,11 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
                   window: int | None, scale: float, out: torch.Tensor | None = None,
                   split_keys: int = SPLIT_KEYS, prefetch: torch.Tensor | None = None,
                   prompt_on_tcgen05: bool = True, decode_on_tcgen05: bool | None = None) -> torch.Tensor:
-    """Tensor-core paged attention for bfloat16 over request segments (see csrc/attention_mma.cu)."""
+    """Tensor-core paged attention for bfloat16 over request segments.  Prompt portions (segments of several tokens)
+    and single tokens are separate kernels: for head sizes 64 / 128 the tcgen05 kernels of csrc/attention_tcgen05.cu
+    (``prompt_on_tcgen05`` / ``decode_on_tcgen05``; the ranges of a split decode are combined by the merge kernel
+    of csrc/attention_mma.cu), otherwise - and for sizes those do not take - the mma.sync kernels of
+    csrc/attention_mma.cu."""
     _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml)
     _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
     if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
