@@ -709,17 +709,36 @@ __global__ void attn_merge_kernel(const AttnParams p, const int* __restrict__ to
     if (p.seg_len[seg] != 1) return;
     const int n = decode_num_splits(p.seg_start[seg], p.window, p.split_keys);
     if (n <= 1) return;
-    const float* ml = p.part_ml + (size_t)row * p.max_splits * 2;
+    const float2* ml = reinterpret_cast<const float2*>(p.part_ml + (size_t)row * p.max_splits * 2);   // (max, sum)
     const float* acc = p.part_acc + (size_t)row * p.max_splits * D;
+    // The ranges are taken eight at a time with all their loads issued before the first use: the loop is a chain
+    // of memory latencies otherwise.  The order of the sums is the order of the ranges.
     float mstar = -INFINITY;
-    for (int s = 0; s < n; ++s) mstar = fmaxf(mstar, ml[2 * s]);
+    for (int s0 = 0; s0 < n; s0 += 8) {
+        float2 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = s0 + i < n ? ml[s0 + i] : make_float2(-INFINITY, 0.0f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mstar = fmaxf(mstar, v[i].x);
+    }
     for (int e = threadIdx.x; e < D; e += blockDim.x) {
         float lsum = 0.0f, a = 0.0f;
         if (mstar != -INFINITY) {
-            for (int s = 0; s < n; ++s) {
-                const float f = exp2f(ml[2 * s] - mstar);
-                lsum += ml[2 * s + 1] * f;
-                a += acc[(size_t)s * D + e] * f;
+            for (int s0 = 0; s0 < n; s0 += 8) {
+                float2 v[8];
+                float x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const bool live = s0 + i < n;
+                    v[i] = live ? ml[s0 + i] : make_float2(-INFINITY, 0.0f);
+                    x[i] = live ? acc[(size_t)(s0 + i) * D + e] : 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float f = exp2f(v[i].x - mstar);      // -inf gives 0
+                    lsum += v[i].y * f;
+                    a += x[i] * f;
+                }
             }
         }
         p.out[(size_t)row * D + e] = __float2bfloat16_rn(lsum > 0.0f ? a / lsum : 0.0f);
