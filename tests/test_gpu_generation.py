@@ -64,6 +64,35 @@ def test_sampled_generation_mixed_batch_config_b(model_folders, graphs):
         assert engine.get_result(rid) == _plain_generate(pc, pw, p, 12, temperature=0.8, seed=100 + i)
 
 
+def test_lookahead_gives_the_same_tokens_as_reading_every_step(model_folders):
+    """bfloat16, head size 64, requests of different lengths that end at different steps (length limits and EOS
+    ids): with a decode step kept in flight the results are those of the plain loop, and steps did stay in flight."""
+    need_gpu()
+    from pulse_infer_b200 import Engine
+    folder, cfg = model_folders["D"], CONFIGS["D"]
+    prompts = [random_tokens(20 + i, n, cfg.vocab_size) for i, n in enumerate((5, 33, 70, 18, 51))]
+    limits = [9, 30, 17, 40, 25]
+    results, in_flight = {}, {}
+    for lookahead in (False, True):
+        engine = Engine(folder, dtype="bfloat16", page_size=16, num_pages=40, max_batch_size=4, chunk_size=32,
+                        lookahead=lookahead)
+        engine.engine.eos_token_ids = (7, 100, 200, 287)          # ids this random model does produce
+        ids = [engine.add_request(p, m, temperature=0.7 if i % 2 else 0.0, top_k=50, seed=5 + i)
+               for i, (p, m) in enumerate(zip(prompts, limits))]
+        count = 0
+        while engine.has_work():
+            engine.step()
+            count += engine.engine._inflight is not None
+        results[lookahead] = [(engine.get_result(i), engine.get_request(i).finish_reason) for i in ids]
+        in_flight[lookahead] = count
+        engine.runner.check_device_errors()
+        engine.runner.cache.check_invariants()
+        assert engine.runner.cache.free_pages() == [40] * len(engine.runner.cache.free_pages())
+    assert results[True] == results[False]
+    assert in_flight[False] == 0 and in_flight[True] >= 10
+    assert {r for _, r in results[True]} <= {"eos", "length"}
+
+
 def test_generation_survives_preemption_and_eos(model_folders):
     """So few pages that requests are preempted and recomputed; tokens are the same as with plenty."""
     need_gpu()
