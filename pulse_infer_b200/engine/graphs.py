@@ -9,6 +9,8 @@ stream (``src/ops/rope.cpp:231``, ``src/ops/matmul.cpp:115``).
 """
 from __future__ import annotations
 
+import gc
+
 import torch
 
 from .. import ops
@@ -68,8 +70,16 @@ class DecodeGraph:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.kernels.LAUNCHES
-            with torch.cuda.graph(graph):
-                self.logits = model.forward(self.ctx)
+            # No garbage collection while the stream is capturing: collecting an old CUDAGraph object (of an engine
+            # that is no longer used) destroys its graph, which is not permitted during a capture and invalidates it.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self.logits = model.forward(self.ctx)
+            finally:
+                if collecting:
+                    gc.enable()
             self.launches_per_replay = ops.kernels.LAUNCHES - before
             self.graph = graph
         self.graph.replay()
