@@ -520,7 +520,9 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 // Two further variants were measured in the same run and dropped: filling the rows of a partial tile from a spare
 // page instead of zeroing the ring at the start (4.04 against 4.00 ms at batch 8, 10.51 against 10.19 at batch 64),
 // and the sums of the probabilities by a product with a tile of ones instead of a reduction across threads at
-// the end of an item (no difference, and shorter key ranges were no faster with it).
+// the end of an item (no difference, and shorter key ranges were no faster with it).  Letting the SMs that a
+// small batch leaves without an item prefetch the output projection's weights into L2 meanwhile made the step
+// slower, not faster (4.12 against 4.04 ms at batch 8).
 // =============================================================================================================
 #define FD_THREADS 192
 #define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
