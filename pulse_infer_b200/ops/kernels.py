@@ -439,6 +439,8 @@ def gemm_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, 
     if K != K2:
         raise KernelError(f"inner sizes differ: {K} vs {K2}")
     lib = _lib("gemm_small_m")
+    if emit_norm is not None and residual is None:
+        raise KernelError("gemm_small_m: preparing the next norm goes with the residual epilogue")
     if not gated and residual is None and row_ssq is None:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)

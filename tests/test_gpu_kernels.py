@@ -476,3 +476,42 @@ def test_logit_edit():
     out = logits.cpu()
     assert out[0, 5] == -1.5 and out[2, 7] == -1.5 and out[2, 99] == -1.5 and out[1, 0] == float("-inf")
     assert out.isfinite().sum() == 299 and (out == 0).sum() == 296
+
+
+def test_kernels_refuse_what_they_do_not_take():
+    """A size or layout a kernel does not take is refused with a message, never computed wrongly."""
+    dev, ops = need_gpu(), _ops()
+    KernelError = ops.KernelError
+    bf = lambda *shape: torch.zeros(*shape, dtype=torch.bfloat16, device=dev)       # noqa: E731
+    i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device=dev)                 # noqa: E731
+    # tcgen05 prompt attention: page sizes 8..128 only, head sizes 64 / 128 only, bfloat16 only
+    kc, vc = bf(4, 2, 4, 64), bf(4, 2, 4, 64)
+    args = (bf(8, 4 * 64), 4 * 64, kc, vc, i32(0, 1).view(1, 2), i32(0), i32(0), i32(0), i32(8), 8, 1, 8, 4, 2, 64)
+    with pytest.raises(KernelError, match="page size"):
+        ops.attention_tcgen05(*args, 4, None, 0.125, bf(8, 4 * 64))
+    with pytest.raises(Exception, match="head size"):
+        ops.attention_tcgen05(bf(8, 4 * 48), 4 * 48, bf(4, 2, 8, 48), bf(4, 2, 8, 48), i32(0, 1).view(1, 2), i32(0), i32(0),
+                              i32(0), i32(8), 8, 1, 8, 4, 2, 48, 8, None, 0.125, bf(8, 4 * 48))
+    with pytest.raises(KernelError, match="bfloat16"):
+        ops.attention_tcgen05(args[0].float(), *args[1:], 8, None, 0.125, bf(8, 4 * 64))
+    assert not ops.attention_tcgen05_usable(96, 16) and not ops.attention_decode_tcgen05_usable(128, 16, 20)
+    assert not ops.attention_decode_tcgen05_usable(128, 128, 4)
+    # weight-streaming product: at most 32 rows, k a multiple of 8, the fused forms only in their combinations
+    w = bf(64, 64)
+    with pytest.raises(KernelError, match="at most 32"):
+        ops.gemm_small_m(bf(33, 64), w, torch.bfloat16)
+    with pytest.raises(KernelError, match="multiples of 8"):
+        ops.gemm_small_m(bf(4, 60), bf(64, 60), torch.bfloat16)
+    with pytest.raises(KernelError, match="gated"):
+        ops.gemm_small_m(bf(4, 64), bf(24, 64), torch.bfloat16, gated=True)          # 24 rows: not whole blocks of 16
+    with pytest.raises(KernelError, match="residual"):
+        ops.gemm_small_m(bf(4, 64), w, torch.float32, residual=torch.zeros(4, 32, device=dev))
+    with pytest.raises(KernelError, match="residual"):
+        ops.gemm_small_m(bf(4, 64), w, torch.bfloat16, emit_norm=bf(64))
+    # tcgen05 product: bfloat16 operands, gated output needs whole blocks
+    with pytest.raises(KernelError, match="bfloat16"):
+        ops.gemm_tcgen05(torch.zeros(4, 64, device=dev), w)
+    with pytest.raises(KernelError, match="gated"):
+        ops.gemm_tcgen05(bf(4, 64), bf(24, 64), torch.bfloat16, gated=True)
+    # nothing above left an error behind
+    assert ops.gemm_tcgen05_status() == 0 and ops.attention_tcgen05_loaded_status() == 0
