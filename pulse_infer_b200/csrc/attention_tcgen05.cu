@@ -522,7 +522,11 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 // and the sums of the probabilities by a product with a tile of ones instead of a reduction across threads at
 // the end of an item (no difference, and shorter key ranges were no faster with it).  Letting the SMs that a
 // small batch leaves without an item prefetch the output projection's weights into L2 meanwhile made the step
-// slower, not faster (4.12 against 4.04 ms at batch 8).
+// slower, not faster (4.12 against 4.04 ms at batch 8).  Two items at a time per CTA (a second group of four
+// softmax warps, the key tiles of the two items alternating through the ring, with the ring shared as it is or cut
+// into separate key and value stages) was correct but slower at every batch size (4.21 / 4.25 against 4.04 ms at
+// batch 8, 11.1 / 11.5 against 10.2 at batch 64): three stages of 64 KB are too few once two tiles are held by
+// softmax groups.
 // =============================================================================================================
 #define FD_THREADS 192
 #define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
