@@ -526,7 +526,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 // softmax warps, the key tiles of the two items alternating through the ring, with the ring shared as it is or cut
 // into separate key and value stages) was correct but slower at every batch size (4.21 / 4.25 against 4.04 ms at
 // batch 8, 11.1 / 11.5 against 10.2 at batch 64): three stages of 64 KB are too few once two tiles are held by
-// softmax groups.
+// softmax groups.  Separate key and value stages in the single-item kernel (keys free again right after S):
+// 10.69 against 10.42 ms at batch 64, 4.09 against 4.07 at batch 8 - twice the barrier traffic for nothing.
 // =============================================================================================================
 #define FD_THREADS 192
 #define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
