@@ -24,7 +24,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# layer sizes of BASELINE.json configs[2] (Qwen3-8B shape)
+# layer sizes of the Qwen3-8B shape
 SHAPE = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
              intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
              max_position_embeddings=40960)
@@ -326,6 +326,73 @@ def run_ours(args) -> dict:
     }
 
 
+def run_reference(args) -> dict:
+    """The reference engine itself on the same shape, batch, context, steps and warm-up: ``baseline/_ref/ref_bench`` is
+    the reference's unmodified sources built for sm_100 by ``baseline/build_reference.py`` plus a driver that calls its
+    ``init_paged_cache`` and ``forward_batched``; nothing of this repository's engine or kernels is on that path."""
+    exe = os.path.join(ROOT, "baseline", "_ref", "ref_bench")
+    if not os.path.isfile(exe):
+        ref = os.environ.get("PULSE_REFERENCE", "/root/reference")
+        if os.path.isdir(os.path.join(ref, "src")):
+            subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "build_reference.py"), "--reference", ref],
+                           stdout=sys.stderr, stderr=sys.stderr)
+    if not os.path.isfile(exe):
+        return {"impl": "reference", "unavailable": "baseline/_ref/ref_bench is not built and no checkout of the reference "
+                "is at hand to build it from (python baseline/build_reference.py --reference DIR)"}
+    layers = args.layers or FULL_LAYERS
+    warmup = max(args.warmup, 3)
+    cmd = [exe, "--layers", str(layers), "--hidden", str(SHAPE["hidden_size"]), "--heads", str(SHAPE["num_attention_heads"]),
+           "--kv-heads", str(SHAPE["num_key_value_heads"]), "--head-dim", str(SHAPE["head_dim"]),
+           "--intermediate", str(SHAPE["intermediate_size"]), "--vocab", str(SHAPE["vocab_size"]),
+           "--max-position", str(SHAPE["max_position_embeddings"]), "--theta", repr(SHAPE["rope_theta"]),
+           "--eps", repr(SHAPE["rms_norm_eps"]), "--batch", str(args.batch), "--context", str(CONTEXT),
+           "--prompt", str(PROMPT), "--steps", str(args.steps), "--warmup", str(warmup), "--page", str(PAGE)]
+    clocks = ClockSampler()
+    clocks.start()
+    t0 = time.monotonic()
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=args.reference_timeout)
+    except subprocess.TimeoutExpired:
+        clocks.stop(t0, time.monotonic())
+        return {"impl": "reference", "unavailable": f"the reference did not finish its run within {args.reference_timeout} s"}
+    clock_info = clocks.stop(t0, time.monotonic())
+    try:
+        out = json.loads(proc.stdout.strip().splitlines()[-1])
+    except (ValueError, IndexError):
+        out = {"error": (proc.stderr or proc.stdout)[-300:]}
+    if proc.returncode != 0 or "error" in out:
+        return {"impl": "reference", "unavailable": f"the reference's run failed (code {proc.returncode}): {out.get('error')}"}
+    peaks, peak_source = load_peaks()
+    cfg = make_config(layers)
+    ms, e2e_ms, prefill_ms = out["decode_ms_per_step"], out["e2e_ms_per_step"], out["prefill_ms"]
+    step_bytes = weight_bytes_per_step(cfg) + kv_bytes(cfg, args.batch, CONTEXT - args.steps / 2.0)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    return {
+        "metric": "decode tok/s (Qwen3-8B shape, bf16, batch 8, context to 4096)",
+        "value": round(args.batch * 1000.0 / ms, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, seeded random weights",
+        "impl": "reference",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": FULL_LAYERS, "hidden": cfg.hidden_size,
+                   "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT, "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (every step reads 15 GB of weights)", "cuda_graphs": False,
+                   "peaks": peak_source},
+        "clocks": clock_info,
+        "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": out["h2d_bytes_per_step"], "d2h_bytes_per_step": out["d2h_bytes_per_step"],
+                "note": "forward_batched + per-request last-row logits to the host + host argmax, as the reference's engine does"},
+        "gpu_launches": None,
+        "prefill": {"value": round(PROMPT * 1000.0 / prefill_ms, 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                    "frac": round(prefill_flops(cfg, PROMPT) / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": {f"decode_b{args.batch}": round(args.batch * 1000.0 / ms, 2)},
+        "fill_s": out.get("fill_s"),
+    }
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -338,11 +405,13 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: the context the timed steps end at")
     ap.add_argument("--prompt-len", type=int, default=None, help="with --only: tokens of each prompt (default 2048)")
     ap.add_argument("--no-graphs", action="store_true", help="with --only: launch decode steps eagerly")
+    ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference is a C++/CMake project without setup.py or "
-                          "pyproject.toml: 'pip install --no-index --target baseline/_ref <the reference>' answers 'not installable', and its "
-                          "CMake build fetches spdlog/json/googletest from the network"}))
+        if args.gpus != 1:
+            print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, only --gpus 1")
+            return 2
+        print(json.dumps(run_reference(args)))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, only --gpus 1")

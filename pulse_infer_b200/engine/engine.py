@@ -108,7 +108,9 @@ class ContinuousBatchEngine:
         """The planned step is one token for each request that sampled in ``prev``, in the same order."""
         if prev.tokens is None or len(batch.entries) != len(prev.sampling_reqs):
             return False
-        return all(n == 1 and req is p and req.unresolved == 1 for (req, n), p in zip(batch.entries, prev.sampling_reqs))
+        return all(n == 1 and req is p and req.unresolved == 1
+                   and req.num_computed_tokens + 1 == req.total_input_tokens()      # the id in flight is what it feeds
+                   for (req, n), p in zip(batch.entries, prev.sampling_reqs))
 
     def _launch(self, batch: ScheduledBatch, tokens_from=None) -> _Launched | None:
         entries = [(req, n) for req, n in batch.entries if not req.is_finished()]     # ended by the read-back just before
@@ -192,7 +194,10 @@ class ContinuousBatchEngine:
                 req.finish("length")
                 finished.append(req.request_id)
         for rid in finished:
-            self.runner.cache.close(rid)
+            # a request that was preempted while its last id was still on its way holds no slot any more (the
+            # scheduler gave its pages back and put it in the waiting queue; update_after_step takes it out there)
+            if self.runner.cache.has(rid):
+                self.runner.cache.close(rid)
         self.scheduler.update_after_step(rec.batch, finished)
         return sampled
 

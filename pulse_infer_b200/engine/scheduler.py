@@ -226,11 +226,15 @@ class ContinuousBatchScheduler:
         self.stats_steps += 1
         for rid in finished_ids:
             req = self.request_map.get(rid)
-            if req is None or req not in self.running_requests:
+            if req is None:
                 continue
-            if not req.is_finished():
-                req.finish()
-            self.running_requests.remove(req)
+            if req in self.running_requests:
+                if not req.is_finished():
+                    req.finish()
+                self.running_requests.remove(req)
+            elif req in self.waiting_queue and req.is_finished():
+                # preempted while a sampled id was still in flight, and that id ended it: nothing is left to recompute
+                self.waiting_queue.remove(req)
 
     def abort(self, request_id: int, reason: str = "aborted") -> None:
         """Take a request out wherever it is; its pages and slot are given back."""
