@@ -28,10 +28,6 @@ class Engine:
         ``lookahead`` (default: on with CUDA graphs): a decode step stays in flight when ``step()`` returns and its
         tokens are read while the next one runs; ``step()`` then returns the tokens of the step before."""
         spec_options = {} if rope_pairing is None else {"rope_pairing": rope_pairing}
-        if num_pages is None and max_tokens is None:
-            from .config.registry import load_config
-            cfg = config if model is None else load_config(model)
-            max_tokens = min(max_batch_size * cfg.max_position_embeddings, 1 << 20)
         self.runner = build_runner(model, config=config, seed=seed, dtype=dtype, device=device, page_size=page_size,
                                    num_pages=num_pages, max_tokens=max_tokens, max_requests=max(max_batch_size, 1),
                                    max_tokens_per_request=max_tokens_per_request,

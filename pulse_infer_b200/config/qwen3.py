@@ -120,6 +120,19 @@ class Qwen3Config(ModelConfig):
                 if kind not in (None, "default"):
                     raise ConfigError(f"'{key}' of type '{kind}' in '{source}' is not supported")
 
+        # What the architecture's config.json can ask for and the parts here cannot do is refused, not ignored.  (The
+        # reference never reads these keys and always computes without biases and with SiLU, model.cpp:208,225,242;
+        # silu_kernel.cu:78-104.)
+        for key in ("attention_bias", "mlp_bias"):
+            if r.bool(key, False):
+                raise ConfigError(f"'{key}': true in '{source}' is not supported: the projections here have no bias")
+        act = r.str("hidden_act", "silu")
+        if act not in ("silu", "swish"):
+            raise ConfigError(f"'hidden_act': '{act}' in '{source}' is not supported: the feed-forward here is SiLU-gated")
+        dropout = r.float("attention_dropout", 0.0)
+        if dropout != 0.0:
+            raise ConfigError(f"'attention_dropout': {dropout} in '{source}' is not supported (inference only)")
+
         layers = r.int("num_hidden_layers")
         window = r.int("sliding_window", None)
         layer_types = r.str_list("layer_types")
@@ -147,7 +160,8 @@ class Qwen3Config(ModelConfig):
         known = {"architectures", "num_attention_heads", "hidden_size", "head_dim", "rope_theta", "num_hidden_layers",
                  "sliding_window", "layer_types", "use_sliding_window", "max_window_layers", "eos_token_id",
                  "intermediate_size", "num_key_value_heads", "vocab_size", "max_position_embeddings",
-                 "rms_norm_eps", "tie_word_embeddings", "torch_dtype", "dtype"}
+                 "rms_norm_eps", "tie_word_embeddings", "torch_dtype", "dtype", "attention_bias", "mlp_bias", "hidden_act",
+                 "attention_dropout"}
         cfg = cls(
             architecture=architecture,
             hidden_size=hidden,

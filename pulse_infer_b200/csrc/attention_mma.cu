@@ -63,6 +63,13 @@ __device__ __forceinline__ int decode_num_splits(int pos, int window, int split_
     const int lo_al = (window_lo(pos, window) / BN) * BN;
     return (pos + 1 - lo_al + split_keys - 1) / split_keys;
 }
+// The ranges a kernel really cuts a request into: never more than the scratch has room for.  When the caller's
+// bound is smaller than the request needs, the last range runs on to the newest key, so every key is still read
+// exactly once and no partial result is written beyond the scratch.
+__device__ __forceinline__ int decode_ranges(int pos, int window, int split_keys, int max_splits) {
+    const int n = decode_num_splits(pos, window, split_keys);
+    return n < max_splits ? n : max_splits;
+}
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -144,10 +151,10 @@ __global__ void __launch_bounds__(ROW_WARPS* KEY_WARPS * 32) attn_mma_kernel(con
     int kend = pos_last + 1;
     int nsplits = 1;
     if (p.decode) {
-        nsplits = decode_num_splits(pos_first, p.window, p.split_keys);
+        nsplits = decode_ranges(pos_first, p.window, p.split_keys, p.max_splits);
         if (split >= nsplits) return;
         kbegin += split * p.split_keys;
-        if (kbegin + p.split_keys < kend) kend = kbegin + p.split_keys;
+        if (split + 1 < nsplits && kbegin + p.split_keys < kend) kend = kbegin + p.split_keys;
     } else if (split > 0) {
         return;
     }
@@ -463,10 +470,10 @@ __global__ void __launch_bounds__(128, (D * NT <= 128) ? 4 : 2) attn_decode_kern
     const int tok = p.seg_off[seg];
     const int* table = p.block_table + (size_t)p.seg_slot[seg] * p.bt_stride;
     const int lo = window_lo(pos, p.window);
-    const int nsplits = decode_num_splits(pos, p.window, p.split_keys);
+    const int nsplits = decode_ranges(pos, p.window, p.split_keys, p.max_splits);
     if (split >= nsplits) return;
     const int kbegin = (lo / BN) * BN + split * p.split_keys;
-    const int kend = min(pos + 1, kbegin + p.split_keys);
+    const int kend = split + 1 < nsplits ? min(pos + 1, kbegin + p.split_keys) : pos + 1;
     const int nslices = (kend - kbegin + 15) / 16;
 
     bf16* vs = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * VSTAGES * 16 * LDS;   // this warp's V stages
@@ -707,7 +714,7 @@ __global__ void attn_merge_kernel(const AttnParams p, const int* __restrict__ to
     const int t = row / p.nq;
     const int seg = token_seg[t];
     if (p.seg_len[seg] != 1) return;
-    const int n = decode_num_splits(p.seg_start[seg], p.window, p.split_keys);
+    const int n = decode_ranges(p.seg_start[seg], p.window, p.split_keys, p.max_splits);
     if (n <= 1) return;
     const float2* ml = reinterpret_cast<const float2*>(p.part_ml + (size_t)row * p.max_splits * 2);   // (max, sum)
     const float* acc = p.part_acc + (size_t)row * p.max_splits * D;
@@ -907,6 +914,14 @@ PI_EXPORT int pi_attention_mma_noalloc(const void* q, int q_stride, const void* 
                                        int window, float scale, cudaStream_t stream) {
     if (num_tokens <= 0 || num_segments <= 0) return 0;
     if (max_splits < 1) return pi_refuse("pi_attention_mma_noalloc: max_splits=%d must be at least 1", max_splits);
+    if (nq <= 0 || nkv <= 0) return pi_refuse("pi_attention_mma_noalloc: nq=%d and nkv=%d must be positive", nq, nkv);
+    // pi_attention_mma also knows has_decode = 2, "another kernel has already left the partial results in the
+    // scratch, only merge them".  Nothing but this entry can write the fixed array, so here that would merge whatever
+    // an earlier call left behind: refused.
+    if (has_decode != 0 && has_decode != 1)
+        return pi_refuse("pi_attention_mma_noalloc: has_decode=%d must be 0 or 1", has_decode);
+    if (has_prompt != 0 && has_prompt != 1)
+        return pi_refuse("pi_attention_mma_noalloc: has_prompt=%d must be 0 or 1", has_prompt);
     // partial outputs [tokens * heads, max_splits, D] followed by (max, sum) pairs [tokens * heads, max_splits, 2]
     const unsigned long long rows = (unsigned long long)num_tokens * (unsigned long long)(nq > 0 ? nq : 0);
     const unsigned long long acc_floats = rows * (unsigned long long)max_splits * PI_HEAD_DIM;

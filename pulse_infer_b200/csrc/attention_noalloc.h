@@ -14,6 +14,8 @@
  *        tokens * query_heads * max_splits * (head_size + 2) * 4   bytes
  *    and is refused (return -1, text from pi_last_error()) when that is more.  Every GPU on which the
  *    library is loaded holds the array until the process exits, whether or not this entry is used.
+ *    The attention library is built once per head size (libpi_attention_mma_d64, ..._d128, ...); each of
+ *    those builds carries an array of its own, so a process that loads three of them holds 24 MiB per GPU.
  *  - No allocation.  The call performs no cudaMalloc, cudaFree or other allocating routine.
  *  - First call.  The first call on each device asks the runtime for the array's device address
  *    (cudaGetSymbolAddress, with that device current).  Make that first call outside any stream capture.
@@ -22,7 +24,9 @@
  *    run at the same time on one GPU - different streams, or different threads - race on it.  Serialise
  *    them, e.g. by launching on one stream.
  *  - Everything else (arguments, results, supported sizes) is exactly pi_attention_mma's; the two scratch
- *    pointers are simply absent.
+ *    pointers are simply absent.  One difference: has_prompt and has_decode must be 0 or 1 here.
+ *    pi_attention_mma's has_decode = 2 ("the partial results are already in the scratch, only merge them")
+ *    is refused, because no other kernel can have written this library's private array.
  */
 #pragma once
 #include <cuda_runtime.h>

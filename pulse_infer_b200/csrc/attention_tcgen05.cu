@@ -557,10 +557,12 @@ __device__ __forceinline__ bool fd_item(const FdParams& p, int it, FdItem& w) {
     w.pos = p.seg_start[w.seg];
     w.lo = fa_window_lo(w.pos, p.window);
     const int lo_al = (w.lo / 64) * 64;
-    w.nsplits = (w.pos + 1 - lo_al + p.split_keys - 1) / p.split_keys;
+    // never more ranges than the scratch has room for: with a bound smaller than the request needs, the last range
+    // runs on to the newest key (the same rule as decode_ranges in attention_mma.cu, whose merge kernel follows)
+    w.nsplits = min((w.pos + 1 - lo_al + p.split_keys - 1) / p.split_keys, p.max_splits);
     if (w.split >= w.nsplits) return false;
     w.kb = lo_al + w.split * p.split_keys;
-    w.ke = min(w.kb + p.split_keys, w.pos + 1);
+    w.ke = w.split + 1 < w.nsplits ? min(w.kb + p.split_keys, w.pos + 1) : w.pos + 1;
     w.ntiles = (w.ke - w.kb + FA_BN - 1) / FA_BN;
     return true;
 }

@@ -41,7 +41,8 @@ def build_runner(model_dir: str | None = None, *, config=None, seed: int | None 
                  use_cuda_graphs: bool = False, **spec_options) -> ModelRunner:
     """From a model folder (``model_dir``) or from a configuration plus a seed (random weights on the
     device) to a ready step function.  The page pool holds ``num_pages`` pages per layer group, or
-    enough for ``max_tokens`` tokens."""
+    enough for ``max_tokens`` tokens (neither given: ``max_requests`` requests of the model's longest context,
+    at most 2^20 tokens)."""
     device = require_cuda(device)
     runtime = Runtime(device, dtype, attention_impl)
     if model_dir is not None:
@@ -63,7 +64,8 @@ def build_runner(model_dir: str | None = None, *, config=None, seed: int | None 
                                 "bfloat16" if runtime.mode == "bfloat16" else "float32")
         if num_pages is None:
             if max_tokens is None:
-                raise ValueError("give num_pages or max_tokens to size the page pool")
+                # every request slot at the model's longest context, capped at a million tokens
+                max_tokens = min(max_requests * model.spec.max_position, 1 << 20)
             num_pages = (max_tokens + page_size - 1) // page_size
         per_request = max_tokens_per_request or min(model.spec.max_position, num_pages * page_size)
         cache = CacheManager(model.cache_specs(), model.state_specs(), page_size, num_pages, max_requests,

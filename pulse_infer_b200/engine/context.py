@@ -67,7 +67,8 @@ class StepContext:
         self.segments: list = []
         self._scratch: dict = {}
         self.splits_bound: int | None = None     # fixed number of key ranges (captured steps)
-        self.split_keys: int | None = None       # fixed keys per range (captured steps); else chosen per step
+        # fixed keys per range (captured steps): {(kv heads, head size): keys}; else chosen per step
+        self.split_keys: dict | None = None
         self.error_count: torch.Tensor | None = None
         self.upcoming_weights = None
         self.prefetch_hints = os.environ.get("PULSE_PREFETCH", "1") != "0"
@@ -141,7 +142,8 @@ class StepContext:
         self.max_seg_len = max(lens) if lens else 0
         self.has_prompt = any(n > 1 for n in lens)
         self.has_decode = any(n == 1 for n in lens)
-        self.decode_pos_max = max([s.start for s in segments if len(s.tokens) == 1], default=0)
+        self.decode_starts = [s.start for s in segments if len(s.tokens) == 1]
+        self.decode_pos_max = max(self.decode_starts, default=0)
         self._scratch = {}
 
     # ---- prefetch hints --------------------------------------------------------------------------------
@@ -175,9 +177,10 @@ class StepContext:
             if not self.has_decode:
                 sc = AttentionScratch(1, None, None)
             else:
-                num_decode = sum(1 for s in self.segments if len(s.tokens) == 1)
-                split_keys = self.split_keys or ops.choose_split_keys(num_decode, num_kv_heads, self.decode_pos_max, head_dim)
-                splits = self.splits_bound or ops.attention_num_splits(self.decode_pos_max, window, split_keys)
+                split_keys = (self.split_keys or {}).get((num_kv_heads, head_dim)) or ops.choose_split_keys(
+                    len(self.decode_starts), num_kv_heads, self.decode_pos_max, head_dim)
+                # the widest request decides: with a window that is not always the one at the highest position
+                splits = self.splits_bound or ops.attention_splits_bound(self.decode_starts, window, split_keys)
                 if splits > 1:
                     rows = self.num_tokens * num_heads
                     acc = torch.empty((rows, splits, head_dim), dtype=torch.float32, device=self.device)

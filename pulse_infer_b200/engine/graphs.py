@@ -25,7 +25,7 @@ def _pow2_at_least(n: int) -> int:
 
 
 class DecodeGraph:
-    def __init__(self, runner, num_requests: int, split_keys: int, splits_bound: int):
+    def __init__(self, runner, num_requests: int, split_keys: tuple, splits_bound: int):
         self.runner = runner
         self.num_requests = num_requests
         self.splits_bound = splits_bound
@@ -40,7 +40,7 @@ class DecodeGraph:
         self.ctx.buffer = torch.zeros(total, dtype=torch.int32, device=device)
         self.ctx.error_count = torch.zeros(1, dtype=torch.int32, device=device)
         self.ctx.splits_bound = splits_bound
-        self.ctx.split_keys = split_keys
+        self.ctx.split_keys = dict(split_keys)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
 
@@ -65,8 +65,15 @@ class DecodeGraph:
             self.ctx.tokens.copy_(tokens_from.reshape(-1))
         if self.graph is None:
             model = self.runner.model
-            # once eagerly (library initialisation, kernel attributes), then capture the same work
+            # Once eagerly (library initialisation, kernel attributes), then capture the same work.  The eager run and
+            # the first replay both compute this step: page writes are idempotent, and fixed-size per-request state
+            # is put back to what it was, so that the replay finds the step's true input there.
+            states = self.runner.cache.state
+            kept = {layer: t.clone() for layer, t in states.items() if t is not None}
             model.forward(self.ctx)
+            for layer, t in kept.items():
+                states[layer].copy_(t)
+            del kept
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.kernels.LAUNCHES
@@ -96,16 +103,25 @@ class DecodeGraphs:
         self.graphs: dict = {}
 
     def eligible(self, segments) -> bool:
+        """A step of single tokens, each wanting its logits, of a model whose parts all allow recording
+        (``parts.base.Part.capturable``); everything else is launched kernel by kernel."""
+        if not getattr(self.runner.model, "capturable", False):
+            return False
         return all(len(s.tokens) == 1 and list(s.want) == [0] for s in segments)
 
     def run(self, segments, tokens_from=None) -> torch.Tensor:
-        specs = [cs for cs in self.runner.model.cache_specs() if cs is not None]
-        windows = {cs.window for cs in specs}
-        pos_max = max(s.start for s in segments)
-        split_keys = ops.choose_split_keys(len(segments), max((cs.num_kv_heads for cs in specs), default=1), pos_max,
-                                           specs[0].head_dim if specs else None)
-        need = max(ops.attention_num_splits(pos_max, w, split_keys) for w in windows) if windows else 1
-        key = (len(segments), split_keys, _pow2_at_least(need))
+        specs = {cs for cs in self.runner.model.cache_specs() if cs is not None}
+        starts = [s.start for s in segments]
+        pos_max = max(starts)
+        # keys per range for every kind of layer (kv heads, head size), and one bound on the ranges for the whole
+        # step: the widest request of the widest kind
+        split_keys = {}
+        for cs in specs:
+            split_keys[(cs.num_kv_heads, cs.head_dim)] = ops.choose_split_keys(len(segments), cs.num_kv_heads, pos_max,
+                                                                               cs.head_dim)
+        need = max((ops.attention_splits_bound(starts, cs.window, split_keys[(cs.num_kv_heads, cs.head_dim)])
+                    for cs in specs), default=1)
+        key = (len(segments), tuple(sorted(split_keys.items())), _pow2_at_least(need))
         g = self.graphs.get(key)
         if g is None:
             if len(self.graphs) >= self.max_graphs:

@@ -81,6 +81,7 @@ class ContinuousBatchScheduler:
         self.running_requests: list = []
         self.request_map: dict = {}
         self._next_request_id = 0
+        self._decode_turn = 0
         self.stats_preemptions = 0
         self.stats_steps = 0
         self.stats_prefill_tokens = 0
@@ -124,26 +125,45 @@ class ContinuousBatchScheduler:
         reserved_end = ((req.num_computed_tokens + page - 1) // page) * page
         room = max(0, reserved_end - req.num_computed_tokens) + free * page
         n = min(tokens, room)
-        while n > 0 and not self._fits(req, n):
-            n -= 1
-        return n
+        if n <= 0 or self._fits(req, n):
+            return max(n, 0)
+        lo, hi = 0, n              # fits(lo) holds (lo = 0 asks for nothing), fits(hi) does not: bisect
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if self._fits(req, mid):
+                lo = mid
+            else:
+                hi = mid
+        return lo
 
-    def _preempt(self, victim: InferenceRequest, batch: ScheduledBatch) -> None:
+    def _preempt(self, victim: InferenceRequest, batch: ScheduledBatch) -> int:
+        """Take ``victim`` out of the running set; returns the tokens it had been given in ``batch`` (they go back
+        into the step's budget)."""
         self.cache.close(victim.request_id)
         victim.preempt()
         self.running_requests.remove(victim)
         self.waiting_queue.appendleft(victim)
         batch.preempted.append(victim)
+        given_back = sum(n for r, n in batch.entries if r is victim)
         batch.entries = [(r, n) for r, n in batch.entries if r is not victim]
         self.stats_preemptions += 1
+        return given_back
 
     def schedule_next_batch(self) -> ScheduledBatch:
         batch = ScheduledBatch()
         budget = self.max_tokens_per_step
+        decode_entries: set = set()
 
-        # 1. decoding requests: one token each; make room by preempting the newest request if need be
-        for req in list(self.running_requests):
-            if req not in self.running_requests or req.is_prefill() or not req.has_pending_input():
+        # 1. decoding requests: one token each; make room by preempting the newest request if need be.  When the
+        # budget is smaller than the number of decoding requests, the starting point moves on from step to step, so
+        # that the same requests are not left out every time.
+        decoding = [r for r in self.running_requests if not r.is_prefill() and r.has_pending_input()]
+        if len(decoding) > budget > 0:
+            turn = self._decode_turn % len(decoding)
+            decoding = decoding[turn:] + decoding[:turn]
+            self._decode_turn += budget
+        for req in decoding:
+            if req not in self.running_requests:
                 continue
             while not self._fits(req, 1):
                 victim = self.running_requests[-1]
@@ -153,13 +173,13 @@ class ContinuousBatchScheduler:
                     req.finish("out_of_pages")
                     batch.failed.append(req)
                     break
-                self._preempt(victim, batch)
+                budget += self._preempt(victim, batch)
                 if victim is req:
                     break
             if req in self.running_requests and budget > 0:
                 self.cache.reserve(req.request_id, req.num_computed_tokens + 1)
                 batch.entries.append((req, 1))
-                self.stats_decode_tokens += 1
+                decode_entries.add(req.request_id)
                 budget -= 1
 
         # 2. running requests that still feed known tokens: portions under the budget and the free pages
@@ -170,7 +190,6 @@ class ContinuousBatchScheduler:
             if n > 0:
                 self.cache.reserve(req.request_id, req.num_computed_tokens + n)
                 batch.entries.append((req, n))
-                self.stats_prefill_tokens += n
                 budget -= n
 
         # 3. admission, first come first served
@@ -197,7 +216,6 @@ class ContinuousBatchScheduler:
             req.start_running()
             self.running_requests.append(req)
             batch.entries.append((req, want))
-            self.stats_prefill_tokens += want
             budget -= want
 
         # a step must make progress: if requests run but nothing was planned, the newest one gives way (unless the
@@ -212,6 +230,11 @@ class ContinuousBatchScheduler:
             else:
                 self._preempt(victim, batch)
                 return self._merge(batch, self.schedule_next_batch())
+        for req, n in batch.entries:          # counted from what is really in the step (preemptions took entries out)
+            if req.request_id in decode_entries:
+                self.stats_decode_tokens += n
+            else:
+                self.stats_prefill_tokens += n
         return batch
 
     @staticmethod

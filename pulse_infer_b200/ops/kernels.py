@@ -272,6 +272,18 @@ def attention_num_splits(pos: int, window: int | None, split_keys: int = SPLIT_K
     return (pos + 1 - lo_al + split_keys - 1) // split_keys
 
 
+def attention_splits_bound(positions, window: int | None, split_keys: int = SPLIT_KEYS) -> int:
+    """The width the scratch of the split decode attention needs for requests whose newest tokens sit at
+    ``positions``: the largest count among them.  Without a window that is the count at the highest position; with
+    one it is not (the window's first key is rounded down to a multiple of 64, so the count swings by one with
+    pos % 64) - every position is looked at."""
+    if not positions:
+        return 1
+    if not window:
+        return attention_num_splits(max(positions), None, split_keys)
+    return max(attention_num_splits(p, window, split_keys) for p in set(positions))
+
+
 TCGEN05_ATTENTION = os.environ.get("PULSE_TCGEN05_ATTENTION", "1") != "0"
 
 

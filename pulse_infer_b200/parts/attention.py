@@ -21,6 +21,7 @@ from .base import CacheSpec, Mixer, TensorSpec, register_part
 
 @register_part("mixer", "attention")
 class Attention(Mixer):
+    capturable = True       # see parts.base.Part.capturable
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, qk_norm: bool = True,
                  norm_eps: float = 1e-6, position: str | None = "rotary", window: int | None = None,
                  scale: float | None = None, writes_cache: bool = True):

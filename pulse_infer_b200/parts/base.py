@@ -46,6 +46,14 @@ class StateSpec:
 
 class Part:
     kind: str = ""
+    # True: ``forward`` may be recorded once into a CUDA graph and replayed for later steps of the same shape.  A part
+    # that says so promises that its forward (1) takes everything that changes from step to step - tokens, positions,
+    # slots, segment starts and lengths - from the device tensors of ``ctx``, never from host values such as
+    # ``ctx.segments`` or a Python loop over requests, (2) launches the same kernels with the same arguments for every
+    # step of that shape, and (3) may run twice on one step's data (a warm-up before the recording) without harm:
+    # whatever it writes is idempotent (pages) or lives in ``cache.state``, which the engine puts back after the
+    # warm-up.  The default is False: a step whose model holds such a part is launched kernel by kernel.
+    capturable: bool = False
 
     def tensor_specs(self) -> dict:
         """name (relative to the part's prefix) -> TensorSpec."""

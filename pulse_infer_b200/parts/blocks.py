@@ -20,6 +20,7 @@ def _fusable(norm):
 
 @register_part("block", "pre_norm")
 class PreNormBlock(Block):
+    capturable = True       # see parts.base.Part.capturable
     def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
         self.mixer = mixer
         self.feed_forward = feed_forward

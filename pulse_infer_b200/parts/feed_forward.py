@@ -19,6 +19,7 @@ from .base import FeedForward, TensorSpec, register_part
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
+    capturable = True       # see parts.base.Part.capturable
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size

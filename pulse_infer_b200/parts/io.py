@@ -14,6 +14,7 @@ from .base import Part, TensorSpec, register_part
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
+    capturable = True       # see parts.base.Part.capturable
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
@@ -29,9 +30,14 @@ class TokenEmbedding(Part):
     def forward(self, tokens: torch.Tensor, ctx) -> torch.Tensor:
         return ops.embed(tokens, self.table)
 
+    def tied_table(self) -> torch.Tensor:
+        """[vocab, hidden]: what a head that shares the embedding's weights multiplies with."""
+        return self.table
+
 
 @register_part("head", "lm_head")
 class LMHead(Part):
+    capturable = True       # see parts.base.Part.capturable
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
@@ -51,6 +57,14 @@ class LMHead(Part):
 
     def tie_to(self, table: torch.Tensor) -> None:
         self.weight = table
+
+    def finish(self, embedding) -> None:
+        """After loading: a tied head without a tensor of its own uses the embedding's table
+        (``src/model/qwen3/model.cpp:1346-1371``); a head that ends up with nothing is an error (``model.cpp:1373``)."""
+        if self.weight is None and self.tied:
+            self.tie_to(embedding.tied_table())
+        if self.weight is None:
+            raise RuntimeError("lm_head is not initialized")
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if self.weight is None:

@@ -88,6 +88,24 @@ class DecoderModel:
     def state_specs(self) -> list:
         return [layer.mixer.state_spec() for layer in self.layers]
 
+    def all_parts(self):
+        """Every part of the model, the blocks and what they are made of included."""
+        yield self.embedding
+        yield from self.positions.values()
+        for block in self.layers:
+            yield block
+            for name in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm"):
+                part = getattr(block, name, None)
+                if part is not None:
+                    yield part
+        yield self.final_norm
+        yield self.lm_head
+
+    @property
+    def capturable(self) -> bool:
+        """Whether a step of this model may be recorded into a CUDA graph: every part must say so."""
+        return all(getattr(part, "capturable", False) for part in self.all_parts())
+
     # ---- weights ----------------------------------------------------------------------------------
     def named_parts(self):
         """(prefix, part) for every part that owns tensors."""
@@ -114,10 +132,10 @@ class DecoderModel:
         return out
 
     def finish_loading(self) -> None:
-        if self.lm_head.weight is None and getattr(self.lm_head, "tied", False):
-            self.lm_head.tie_to(self.embedding.table)
-        if self.lm_head.weight is None:
-            raise RuntimeError("lm_head is not initialized")
+        """Called once all tensors are in: the head may now borrow what it ties to from the embedding."""
+        finish = getattr(self.lm_head, "finish", None)
+        if finish is not None:
+            finish(self.embedding)
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -13,6 +13,7 @@ from .base import Norm, TensorSpec, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
+    capturable = True       # see parts.base.Part.capturable
     def __init__(self, size: int, eps: float):
         self.size = size
         self.eps = float(eps)

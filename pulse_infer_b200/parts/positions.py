@@ -16,6 +16,7 @@ from .base import PositionEncoding, register_part
 
 @register_part("position_encoding", "rotary")
 class RotaryEncoding(PositionEncoding):
+    capturable = True       # see parts.base.Part.capturable
     def __init__(self, theta: float, rotary_dim: int, pairing: str = "adjacent"):
         if rotary_dim <= 0 or rotary_dim % 2:
             raise ValueError(f"rotary_dim must be positive and even, got {rotary_dim}")

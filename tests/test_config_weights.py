@@ -66,6 +66,19 @@ def test_config_validation(tmp_path):
         load_config(str(tmp_path / "empty"))
 
 
+@pytest.mark.parametrize("patch, word", [
+    ({"attention_bias": True}, "attention_bias"), ({"mlp_bias": True}, "mlp_bias"),
+    ({"hidden_act": "gelu"}, "hidden_act"), ({"attention_dropout": 0.1}, "attention_dropout")])
+def test_config_refuses_what_the_parts_cannot_compute(tmp_path, patch, word):
+    """A key of the architecture's own config.json that asks for something the parts here do not do is an error that
+    names the key - never a model silently computed without it."""
+    with pytest.raises(ConfigError, match=word):
+        load_config(_write(tmp_path, {**BASE, **patch}))
+    # the same keys with the values that the parts do compute are accepted
+    ok = {"attention_bias": False, "mlp_bias": False, "hidden_act": "silu", "attention_dropout": 0.0}
+    assert load_config(_write(tmp_path, {**BASE, **ok})).hidden_size == 64
+
+
 def test_config_window_keys(tmp_path):
     cfg = load_config(_write(tmp_path, {**BASE, "num_hidden_layers": 4, "use_sliding_window": True,
                                         "sliding_window": 32, "max_window_layers": 2}))

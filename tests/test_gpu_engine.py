@@ -1,5 +1,5 @@
 """The engine against the plain implementation: every way of cutting the same requests into steps,
-in 32-bit and in bfloat16, on three tiny configurations that differ in every size and option."""
+in 32-bit and in bfloat16, on tiny configurations that differ in every size and option."""
 import json
 import os
 import subprocess
@@ -51,7 +51,7 @@ def _plain(plain_cache, folder, tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_then_last_32_one_by_one_then_portions(name, dtype, model_folders, plain_cache):
     from pulse_infer_b200.engine import Segment
     need_gpu()
@@ -91,12 +91,13 @@ def test_whole_then_last_32_one_by_one_then_portions(name, dtype, model_folders,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_prompt_in_large_portions(dtype, model_folders, plain_cache):
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_long_prompt_in_large_portions(name, dtype, model_folders, plain_cache):
     """Portions of several hundred tokens: several query tiles over several key tiles, a window that ends inside
-    a key tile (head size 64: the tcgen05 attention kernel in bfloat16), then single tokens."""
+    a key tile (head sizes 64 and 128: the tcgen05 attention kernel in bfloat16), then single tokens."""
     from pulse_infer_b200.engine import Segment
     need_gpu()
-    folder, cfg = model_folders["D"], CONFIGS["D"]
+    folder, cfg = model_folders[name], CONFIGS[name]
     toks = random_tokens(77, 600, cfg.vocab_size)
     want = _plain(plain_cache, folder, toks)
     runner = _runner(folder, dtype, num_pages=48, max_tokens_per_request=768)
@@ -112,7 +113,7 @@ def test_long_prompt_in_large_portions(dtype, model_folders, plain_cache):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_mixed_batches_with_reused_pages(name, dtype, model_folders, plain_cache):
     """Up to four live requests, portions of some beside decoded tokens of others, in a pool so small
     that pages of finished requests are handed to the next ones at once."""

@@ -343,3 +343,44 @@ def test_lookahead_random_workloads_match_an_unconstrained_run(seed):
         assert seen.get(rid, []) == engine.get_result(rid)             # every token was handed out once, in order
         assert engine.get_request(rid).unresolved == 0
     assert cache.free_pages() == [cache.num_pages] and cache.num_free_slots == 8
+
+
+def test_small_budget_rotates_over_decoding_requests_and_stats_count_what_ran():
+    """Four decoding requests under a budget of two tokens a step: nobody starves, and the counters equal the tokens
+    that the model really saw."""
+    engine, model, cache = make_engine(max_batch_size=4, chunk_size=8, max_tokens_per_step=2)
+    prompts = [[1 + i, 2, 3] for i in range(4)]
+    ids = [engine.add_request(p, 6) for p in prompts]
+    served = {rid: 0 for rid in ids}
+    while engine.has_work():
+        engine.step()
+        assert engine.last_batch.num_tokens <= 2
+        decoding = [r for r in engine.last_batch.requests if r.num_generated() > 1]
+        for r in decoding:
+            served[r.request_id] += 1
+    for rid, p in zip(ids, prompts):
+        assert engine.get_result(rid) == expected_output(p, 6)
+    st = engine.get_stats()
+    ran = sum(n for step in model.steps for _, _, n in step)
+    assert st.prefill_tokens + st.decode_tokens == ran
+    assert st.prefill_tokens == sum(len(p) for p in prompts) and st.decode_tokens == 4 * 5
+    # while all four were decoding, consecutive steps served different pairs
+    pairs = [tuple(sorted(r for r, s, n in step)) for step in model.steps if all(n == 1 and s >= 3 for r, s, n in step)]
+    assert len(set(pairs[:4])) > 1
+
+
+def test_preempting_a_request_already_in_the_step_gives_its_token_back():
+    """Pages run out while the decode loop plans: a victim that already had its token in this step is taken out, and
+    both the step's budget and the counters forget that token."""
+    engine, model, cache = make_engine(num_pages=5, page_size=4, max_batch_size=3, chunk_size=16, max_tokens_per_step=3)
+    a = engine.add_request([1, 2, 3, 4, 5, 6, 7], 9)      # 2 pages, a third at length 9
+    b = engine.add_request([9, 8, 7, 6, 5, 4, 3], 9)
+    engine.run_until_complete()
+    for rid, p in ((a, [1, 2, 3, 4, 5, 6, 7]), (b, [9, 8, 7, 6, 5, 4, 3])):
+        r = engine.get_request(rid)
+        want = expected_output(p, 9)
+        got = engine.get_result(rid)
+        assert got == (want if r.finish_reason != "out_of_pages" else want[:len(got)])
+    st = engine.get_stats()
+    assert st.num_preemptions > 0
+    assert st.prefill_tokens + st.decode_tokens == sum(n for step in model.steps for _, _, n in step)
