@@ -71,6 +71,19 @@ static int pi_pdl_enabled() {
     return enabled;
 }
 
+// Streaming multiprocessors of the current device (asked once); launch shapes are sized from it.
+static int pi_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0, n = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0)
+            return 1;
+        sms = n;
+    }
+    return sms;
+}
+
 template <typename... Params, typename... Args>
 static void pi_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};

@@ -232,11 +232,11 @@ static void launch_small_m(const void* x, int ldx, const void* W, int ldw, void*
     const int tiles = (N + SM_FEATURES - 1) / SM_FEATURES;
     if (variant == 0) {   // from measurements on B200 at the sizes of 8B- to 32B-class models
         if (MT == 1) {
-            if (tiles <= 2 * 148) variant = K >= 8192 ? 3 : 1;   // few tiles: deep K wants more warps per tile
+            if (tiles <= 2 * pi_sm_count()) variant = K >= 8192 ? 3 : 1;   // few tiles: deep K wants more warps per tile
             else if (tiles <= 1000) variant = 2;
             else variant = 4;                                    // many waves: light CTAs, four per SM
         } else {
-            variant = tiles <= 2 * 148 ? 1 : 2;
+            variant = tiles <= 2 * pi_sm_count() ? 1 : 2;
         }
     }
     if (variant == 3 && MT != 1) variant = 1;

@@ -25,7 +25,9 @@
 #define TC_BM 128
 #define TC_BK 64            // 64 bf16 = 128 bytes = one swizzle row
 #define TC_THREADS 192
-#define TC_SPIN_LIMIT (1u << 22)
+#ifndef TC_SPIN_LIMIT
+#define TC_SPIN_LIMIT (1u << 22)      // polls before a wait gives up (a test build sets a smaller number)
+#endif
 
 // ---- status word ---------------------------------------------------------------------------------------
 // 0: fine.  Otherwise (code << 24) | detail of the first wait that ran out.
@@ -123,6 +125,9 @@ struct TcParams {
     int out_f32;     // 1: float32 output, 0: bfloat16
     int gated;       // 1: W rows come in blocks of 16, 8 gate features and their 8 up features; see the epilogue
     int tiles_m, tiles_n;
+#ifdef TC_TEST_HOOKS
+    int skip_load;   // test builds only: the pipeline iteration whose loads the producer leaves out (-1: none)
+#endif
 };
 
 // One 32-column chunk of an accumulator row goes to memory: plain (bf16 or f32), or through the gated activation.
@@ -211,6 +216,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const unsigned s = it % STAGES, round = it / STAGES;
                     if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, (1u << 24) | it, failed)) break;
+#ifdef TC_TEST_HOOKS
+                    if ((int)it == p.skip_load) continue;      // nothing will ever complete this stage: the consumer's wait runs out
+#endif
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                     tma_load_2d(sA + s * A_BYTES, &map_x, kt * TC_BK, m0, &full[s]);
                     tma_load_2d(sB + s * B_BYTES, &map_w, kt * TC_BK, n0, &full[s]);
@@ -535,6 +543,14 @@ PI_EXPORT int pi_gemm_tcgen05_status(unsigned* status) {
     return 0;
 }
 
+#ifdef TC_TEST_HOOKS
+// Test builds only (-DTC_TEST_HOOKS, never the library the engine loads): the next single-CTA launch leaves out
+// the loads of pipeline iteration `it`, so that the wait for that stage runs out and the give-up path executes.
+static int g_test_skip_load = -1;
+PI_EXPORT void pi_gemm_tcgen05_test_skip_load(int it) { g_test_skip_load = it; }
+PI_EXPORT unsigned pi_gemm_tcgen05_spin_limit() { return TC_SPIN_LIMIT; }
+#endif
+
 // gated = 1: W holds gate and up rows interleaved in blocks of 8 (rows 16b .. 16b+7 gate features 8b .. 8b+7,
 // rows 16b+8 .. 16b+15 the matching up features); out is [M, N / 2] bf16 = silu(gate) * up.
 // mode 0: CTA pairs when M > 128, single CTAs otherwise; 1: single CTAs; 2: CTA pairs
@@ -555,18 +571,22 @@ PI_EXPORT int pi_gemm_tcgen05(const void* x, int ldx, const void* W, int ldw, vo
     if (rc) return rc;
     TcParams p;
     p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = out_dtype == PI_F32; p.gated = gated;
+#ifdef TC_TEST_HOOKS
+    p.skip_load = pairs_mode ? -1 : g_test_skip_load;
+    g_test_skip_load = -1;
+#endif
     if (pairs_mode) {
         p.tiles_m = (M + 255) / 256;
         p.tiles_n = (N + BN - 1) / BN;
         int pairs = p.tiles_m * p.tiles_n;
-        const int limit = (max_ctas > 0 ? max_ctas : 148) / 2;
+        const int limit = (max_ctas > 0 ? max_ctas : pi_sm_count()) / 2;
         if (pairs > limit) pairs = limit > 0 ? limit : 1;
         return tc_launch_2cta<6>(mx, mw, p, pairs, stream);
     }
     p.tiles_m = (M + TC_BM - 1) / TC_BM;
     p.tiles_n = (N + BN - 1) / BN;
     int ctas = p.tiles_m * p.tiles_n;
-    const int limit = max_ctas > 0 ? max_ctas : 148;
+    const int limit = max_ctas > 0 ? max_ctas : pi_sm_count();
     if (ctas > limit) ctas = limit;
     return tc_launch<256, 4>(mx, mw, p, ctas, stream);
 }

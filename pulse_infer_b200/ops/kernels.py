@@ -238,6 +238,18 @@ def attention_simple(q: torch.Tensor, q_stride: int, kcache, vcache, block_table
     return out
 
 
+_SM_COUNT: int | None = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current CUDA device (148 on a B200); launch shapes are sized from it."""
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        _SM_COUNT = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
+            if torch.cuda.is_available() else 148
+    return _SM_COUNT
+
+
 def choose_split_keys(num_decode: int, num_kv_heads: int, max_pos: int, head_dim: int | None = None) -> int:
     """Keys per range of the split decode attention (from measurements on B200).
     The persistent tcgen05 kernel (head sizes 64 / 128) wants about one item per SM and as few ranges as that
@@ -248,17 +260,19 @@ def choose_split_keys(num_decode: int, num_kv_heads: int, max_pos: int, head_dim
         return int(forced)
     if TCGEN05_DECODE and TCGEN05_ATTENTION and head_dim in (64, 128):
         pairs = num_decode * max(num_kv_heads, 1)
+        items = sm_count() * 120 // 148          # about four fifths of the SMs busy before ranges get longer
         for keys in (2048, 1024, 512):
-            if pairs * (max_pos + 1) >= 120 * keys:
+            if pairs * (max_pos + 1) >= items * keys:
                 return keys
         return SPLIT_KEYS
     tiles = (max_pos + 256) // 256
     ctas = num_decode * max(num_kv_heads, 1) * tiles
-    if ctas > 48 * 148:
+    sms = sm_count()
+    if ctas > 48 * sms:
         return 2048
-    if ctas > 16 * 148:
+    if ctas > 16 * sms:
         return 1024
-    if ctas > 6 * 148:
+    if ctas > 6 * sms:
         return 512
     return SPLIT_KEYS
 

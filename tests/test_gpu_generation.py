@@ -344,6 +344,60 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     logits = runner.step([Segment("c", reqs["b"], list(range(23)))]).cpu().double().numpy()
     assert np.abs(logits - want["b"]).max() <= 2e-5 * np.abs(want["b"]).max()
 
+    # ---- through the entry point, where recording of decode steps is on by default ---------------------------------
+    # Three requests of different lengths and limits: the set of slots in a two-request decode step changes while
+    # steps of that shape have already run.  DecaySum walks ctx.segments on the host, so it does not declare itself
+    # capturable and its steps are launched kernel by kernel; the tokens are the plain implementation's.
+    from pulse_infer_b200 import Engine
+    prompts = [random_tokens(7, 5, cfg.vocab_size), random_tokens(8, 11, cfg.vocab_size), random_tokens(9, 17, cfg.vocab_size)]
+    limits = [12, 7, 15]
+
+    def plain_greedy(prompt, n):
+        toks = list(prompt)
+        for _ in range(n):
+            toks.append(plain_model.greedy(plain_toy(toks)[-1]))
+        return toks[len(prompt):]
+    want_tokens = [plain_greedy(p, n) for p, n in zip(prompts, limits)]
+    eng = Engine(folder, dtype="float32", page_size=8, num_pages=32, max_batch_size=3, use_cuda_graphs=True)
+    assert not eng.runner.model.capturable
+    ids = [eng.add_request(p, n, ignore_eos=True) for p, n in zip(prompts, limits)]
+    eng.run_until_complete()
+    assert [eng.get_result(i) for i in ids] == want_tokens
+    assert not eng.runner.graphs.graphs                      # nothing was recorded
+
+    # The same mixer written so that a recorded step stays right: for steps of single tokens it reads the slots from
+    # the device (ctx.seg_slot) and updates the state with device-side gathers and scatters; it says capturable.
+    # The engine's warm-up run before the recording must not advance the state twice.
+    class DecaySumDevice(DecaySum):
+        capturable = True
+
+        def forward(self, x, ctx, cache):
+            if ctx.max_seg_len > 1:                           # portions: not recorded, the host loop will do
+                return DecaySum.forward(self, x, ctx, cache)
+            slots = ctx.seg_slot.long()
+            s = self.decay * cache.state.index_select(0, slots) + x.float()
+            cache.state.index_copy_(0, slots, s)
+            return ops.linear(s.to(x.dtype), self.w, ctx.act_dtype)
+
+    if "decay_sum_device" not in MIXERS:
+        register_part("mixer", "decay_sum_device")(DecaySumDevice)
+
+    def build_toy_device_spec(config):
+        spec = build_toy_spec(config)
+        layers = list(spec.layers)
+        layers[1] = dataclasses.replace(layers[1], mixer=dataclasses.replace(layers[1].mixer, kind="decay_sum_device"))
+        return dataclasses.replace(spec, layers=tuple(layers))
+
+    register_architecture("ToyStateDeviceForCausalLM", ToyConfig, build_toy_device_spec, replace=True)
+    cfg2 = dataclasses.replace(cfg, architecture="ToyStateDeviceForCausalLM")
+    folder2 = write_random_model(cfg2, 5, str(tmp_path / "toy_device"), dtype="bfloat16")
+    eng = Engine(folder2, dtype="float32", page_size=8, num_pages=32, max_batch_size=3, use_cuda_graphs=True)
+    assert eng.runner.model.capturable
+    ids = [eng.add_request(p, n, ignore_eos=True) for p, n in zip(prompts, limits)]
+    eng.run_until_complete()
+    assert [eng.get_result(i) for i in ids] == want_tokens
+    assert {key[0] for key in eng.runner.graphs.graphs} >= {1, 2, 3}      # decode steps of 3, 2 and 1 requests were recorded
+
 
 # ---- a toy feed-forward with routing and a toy position encoding, registered from the test ------------------------
 def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path):

@@ -322,6 +322,55 @@ def test_gemm_tcgen05(M, N, K, out_dtype):
     assert ops.gemm_tcgen05_status() == 0 and torch.equal(again, out)
 
 
+def test_gemm_tcgen05_wait_that_runs_out_is_reported_and_the_next_launch_works(monkeypatch, model_folders):
+    """The give-up path of the bounded waits, made to run: a test build of the product (a small poll limit, and a
+    hook that makes the producer leave out the loads of one pipeline stage - a barrier that nothing completes) is
+    put in place of the engine's library.  The launch returns, the status word names the wait of the MMA warp on that
+    stage, the step function's error check raises, and the launch after that is right again with status 0.
+    Nothing traps and nothing spins without a limit: every role falls through to the common exit, which frees the
+    tensor memory; no copy and no MMA is in flight at that point (the only loads of the problem were left out)."""
+    import ctypes
+    dev, ops = need_gpu(), _ops()
+    from pulse_infer_b200.csrc import build
+    from pulse_infer_b200.engine import StepError
+    from test_gpu_engine import _runner
+    monkeypatch.setenv("PULSE_NVCC_FLAGS", "-DTC_TEST_HOOKS -DTC_SPIN_LIMIT=65536")
+    test_lib = ctypes.CDLL(build.library_path("gemm_tcgen05"))
+    monkeypatch.delenv("PULSE_NVCC_FLAGS")
+    test_lib.pi_last_error.restype = ctypes.c_char_p
+    test_lib.pi_gemm_tcgen05_spin_limit.restype = ctypes.c_uint
+    assert test_lib.pi_gemm_tcgen05_spin_limit() == 65536
+    regular = ops.kernels._lib("gemm_tcgen05")
+    with pytest.raises(AttributeError):
+        regular.pi_gemm_tcgen05_test_skip_load                                   # the engine's library has no such hook
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(128, 64, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    w = (torch.randn(256, 64, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    want = (x.double() @ w.double().t()).cpu()
+    runner = _runner(model_folders["D"], "bfloat16")
+    assert ops.gemm_tcgen05_status() == 0
+    monkeypatch.setitem(ops.kernels._LIBS, ("gemm_tcgen05", None), test_lib)
+    # a normal launch of the test build is right
+    out = ops.gemm_tcgen05(x, w, torch.float32)
+    assert ops.gemm_tcgen05_status() == 0
+    assert float((out.cpu().double() - want).abs().max()) <= 1e-5 * float(want.abs().max()) + 1e-6
+    # the next launch leaves out the loads of its only stage (one tile, one k step)
+    test_lib.pi_gemm_tcgen05_test_skip_load(ctypes.c_int(0))
+    ops.gemm_tcgen05(x, w, torch.float32, out=torch.zeros_like(out))
+    torch.cuda.synchronize()                                                  # the kernel gave up and returned
+    with pytest.raises(StepError, match="tcgen05 product"):
+        runner.check_device_errors()                                          # reads (and clears) the status word
+    # what the status word held: code 3 (MMA warp waiting for a loaded stage), iteration 0
+    test_lib.pi_gemm_tcgen05_test_skip_load(ctypes.c_int(0))
+    ops.gemm_tcgen05(x, w, torch.float32, out=torch.zeros_like(out))
+    assert ops.gemm_tcgen05_status() == (3 << 24) | 0
+    # and the launch after it works, status 0
+    out = ops.gemm_tcgen05(x, w, torch.float32)
+    assert ops.gemm_tcgen05_status() == 0
+    assert float((out.cpu().double() - want).abs().max()) <= 1e-5 * float(want.abs().max()) + 1e-6
+    runner.check_device_errors()
+
+
 @pytest.mark.parametrize("M,I,K", [(1, 224, 192), (8, 12288, 256), (5, 8, 64), (16, 1000, 520), (32, 176, 4096)])
 def test_gemm_small_m_gated_epilogue(M, I, K):
     """The weight-streaming product with SiLU(gate) * up as its epilogue, against float64."""
