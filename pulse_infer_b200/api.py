@@ -21,9 +21,10 @@ class Engine:
                  max_tokens: int | None = None, max_batch_size: int = 8, chunk_size: int = 256,
                  max_tokens_per_step: int | None = None, max_tokens_per_request: int | None = None,
                  use_cuda_graphs: bool = True, attention_impl: str = "auto", rope_pairing: str | None = None,
-                 lookahead: bool | None = None):
+                 lookahead: bool | None = None, kv_bytes: int | None = None):
         """``model``: folder with config.json and safetensors; or ``config`` + ``seed`` for random weights.
-        The page pool is ``num_pages`` pages of ``page_size`` tokens, or enough for ``max_tokens`` tokens
+        The page pool is ``num_pages`` pages of ``page_size`` tokens, or what fits in ``kv_bytes`` bytes, or enough
+        for ``max_tokens`` tokens
         (default: ``max_batch_size`` requests of the model's longest context, capped at 1M tokens).
         ``lookahead`` (default: on with CUDA graphs): a decode step stays in flight when ``step()`` returns and its
         tokens are read while the next one runs; ``step()`` then returns the tokens of the step before."""
@@ -32,7 +33,7 @@ class Engine:
                                    num_pages=num_pages, max_tokens=max_tokens, max_requests=max(max_batch_size, 1),
                                    max_tokens_per_request=max_tokens_per_request,
                                    max_tokens_per_step=None, attention_impl=attention_impl,
-                                   use_cuda_graphs=use_cuda_graphs, **spec_options)
+                                   use_cuda_graphs=use_cuda_graphs, kv_bytes=kv_bytes, **spec_options)
         self.config = self.runner.config
         self.sampler = Sampler(self.runner.runtime.device)
         self.engine = ContinuousBatchEngine(self.runner, self.sampler, getattr(self.config, "eos_token_ids", ()),

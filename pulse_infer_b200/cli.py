@@ -51,6 +51,10 @@ def _common(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--num-pages", type=int, default=None)
+    ap.add_argument("--kv-gb", type=float, default=None, help="size the page pool by memory (GiB) instead of --num-pages")
+    ap.add_argument("--max-tokens-per-step", type=int, default=None, help="token budget of one step (default: batch x chunk)")
+    ap.add_argument("--print-logits-topk", type=int, default=0, metavar="K",
+                    help="with every generated token, print the K largest logits it was chosen from")
     ap.add_argument("--no-cuda-graphs", action="store_true")
     ap.add_argument("--device", default="cuda:0")
 
@@ -68,9 +72,11 @@ def _make_engine(args, max_batch_size: int, chunk_size: int, num_pages: int | No
     from .config.registry import get_architecture, load_config
     from .config.base import read_json_file
     pairing = "adjacent" if args.rope_style == "interleaved" else "half"
-    kw = dict(dtype=args.dtype, device=args.device, page_size=args.page_size, num_pages=num_pages, max_tokens=max_tokens,
+    kv_bytes = int(args.kv_gb * (1 << 30)) if args.kv_gb and not num_pages else None
+    kw = dict(dtype=args.dtype, device=args.device, page_size=args.page_size, num_pages=num_pages,
+              max_tokens=None if kv_bytes else max_tokens, kv_bytes=kv_bytes,
               max_batch_size=max_batch_size, chunk_size=chunk_size, use_cuda_graphs=not args.no_cuda_graphs,
-              rope_pairing=pairing)
+              rope_pairing=pairing, max_tokens_per_step=args.max_tokens_per_step)
     if args.random_config:
         from .config.registry import architecture_name_of
         obj = read_json_file(args.random_config)
@@ -81,6 +87,21 @@ def _make_engine(args, max_batch_size: int, chunk_size: int, num_pages: int | No
     if model_dir is None:
         raise SystemExit("no model folder given and no model/ folder found upward from here")
     return Engine(model_dir, **kw), load_config(model_dir)
+
+
+def _topk_recorder(engine, k: int) -> dict:
+    """Make the engine note, for every token it samples, the k largest logits of that position:
+    request id -> list (one entry per generated token) of [[token id, logit], ...]."""
+    import torch
+    seen: dict = {}
+
+    def hook(requests, logits):
+        values, ids = torch.topk(logits, min(k, logits.shape[1]), dim=-1)
+        values, ids = values.tolist(), ids.tolist()
+        for req, v, i in zip(requests, values, ids):
+            seen.setdefault(req.request_id, []).append([[int(t), round(float(x), 5)] for t, x in zip(i, v)])
+    engine.engine.logits_hook = hook
+    return seen
 
 
 def _config_first(args):
@@ -114,12 +135,18 @@ def qwen3_infer(argv=None) -> int:
         temperature = 0.0
     longest = max(len(p) for p in prompts) + max_new
     engine, _ = _make_engine(args, 1, 256, args.num_pages, None if args.num_pages else longest + args.page_size)
+    topk = _topk_recorder(engine, args.print_logits_topk) if args.print_logits_topk > 0 else None
     generated, t0 = 0, time.perf_counter()
     for i, prompt in enumerate(prompts):
-        out = engine.generate([prompt], max_new, temperature=temperature, top_k=top_k, top_p=top_p,
-                              presence_penalty=args.presence_penalty, seed=args.seed + i, ignore_eos=args.ignore_eos)[0]
+        rid = engine.add_request(prompt, max_new, temperature=temperature, top_k=top_k, top_p=top_p,
+                                 presence_penalty=args.presence_penalty, seed=args.seed + i, ignore_eos=args.ignore_eos)
+        engine.run_until_complete()
+        out = engine.get_result(rid)
         generated += len(out)
-        print(json.dumps({"prompt": i, "prompt_tokens": len(prompt), "generated": out}))
+        line = {"prompt": i, "prompt_tokens": len(prompt), "generated": out}
+        if topk is not None:
+            line["logits_topk"] = topk.get(rid, [])[:len(out)]
+        print(json.dumps(line))
     dt = time.perf_counter() - t0
     print(f"Generated {generated} tokens in {dt:.3f}s ({generated / dt:.2f} tokens/s)")
     return 0
@@ -130,7 +157,6 @@ def qwen3_continuous_batch_demo(argv=None) -> int:
     _common(ap)
     ap.add_argument("--max-batch-size", type=int, default=2)
     ap.add_argument("--chunk-size", type=int, default=64)
-    ap.add_argument("--max-tokens-per-step", type=int, default=None)
     ap.add_argument("--temperature", type=float, default=0.0)
     args = ap.parse_args(argv)
     cfg = _config_first(args)
@@ -140,9 +166,9 @@ def qwen3_continuous_batch_demo(argv=None) -> int:
     max_new = [96, 72, 96] if args.max_new_tokens is None else [args.max_new_tokens]
     max_new = [max_new[i % len(max_new)] for i in range(len(prompts))]
     estimate = sum(len(p) + m + 16 for p, m in zip(prompts, max_new))
-    num_pages = args.num_pages or max(64, (estimate + args.page_size - 1) // args.page_size)
+    num_pages = args.num_pages or (None if args.kv_gb else max(64, (estimate + args.page_size - 1) // args.page_size))
     engine, _ = _make_engine(args, args.max_batch_size, args.chunk_size, num_pages, None)
-    engine.engine.scheduler.max_tokens_per_step = args.max_tokens_per_step or args.max_batch_size * args.chunk_size
+    topk = _topk_recorder(engine, args.print_logits_topk) if args.print_logits_topk > 0 else None
     ids = [engine.add_request(p, m, temperature=args.temperature, seed=args.seed + i, ignore_eos=args.ignore_eos)
            for i, (p, m) in enumerate(zip(prompts, max_new))]
     t0 = time.perf_counter()
@@ -158,8 +184,11 @@ def qwen3_continuous_batch_demo(argv=None) -> int:
     for i, rid in enumerate(ids):
         out = engine.get_result(rid)
         total += len(out)
-        print(json.dumps({"request": rid, "prompt_tokens": len(prompts[i]), "generated": out,
-                          "finish_reason": engine.get_request(rid).finish_reason}))
+        line = {"request": rid, "prompt_tokens": len(prompts[i]), "generated": out,
+                "finish_reason": engine.get_request(rid).finish_reason}
+        if topk is not None:
+            line["logits_topk"] = topk.get(rid, [])[:len(out)]
+        print(json.dumps(line))
     st = engine.get_stats()
     print(f"Generated {total} tokens in {dt:.3f}s ({total / dt:.2f} tokens/s); steps={st.num_steps} "
           f"preemptions={st.num_preemptions}")

@@ -46,16 +46,6 @@
 
 __device__ unsigned g_fa_status;
 
-// -DFA_PROFILE: the first CTA adds the cycles it spends at each wait and in each phase to g_fa_prof
-#ifdef FA_PROFILE
-__device__ unsigned long long g_fa_prof[16];
-#define FA_T0() long long fa_t0 = clock64()
-#define FA_ACC(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { long long t = clock64(); atomicAdd(&g_fa_prof[i], (unsigned long long)(t - fa_t0)); fa_t0 = t; } } while (0)
-#else
-#define FA_T0() do {} while (0)
-#define FA_ACC(i) do {} while (0)
-#endif
-
 struct FaParams {
     const bf16* q; int q_stride;
     const int* block_table; int bt_stride;
@@ -335,9 +325,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
             for (int isv = 0; isv < 2; ++isv) {
                 const int n = 2 * j + isv, st = n % FA_STAGES, use = n / FA_STAGES;
-                FA_T0();
                 if (use > 0 && !fa_mbar_wait(&empty[st], (use - 1) & 1, (1u << 24) | n, failed)) { ok = false; break; }
-                FA_ACC(isv);
                 if (lane == 0) fa_mbar_expect_tx(&full[st], bytes);
                 __syncwarp();
                 if (page >= 0) {
@@ -375,15 +363,11 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             }
             for (int j = 0; j < num_tiles && ok && !*failed; ++j) {
                 const bool have_next = j + 1 < num_tiles;
-                FA_T0();
                 if (!wait_full(2 * j + 1)) break;                      // V(j)
-                FA_ACC(3);
                 if (have_next && !wait_full(2 * j + 2)) break;         // K(j + 1)
-                FA_ACC(4);
                 const unsigned char* vt = sKV + ((2 * j + 1) % FA_STAGES) * TILE_BYTES;
                 for (int x = 0; x < nx; ++x) {
                     if (!fa_mbar_wait(&p_ready[x], j & 1, (4u << 24) | (x << 20) | j, failed)) { ok = false; break; }
-                    FA_ACC(5 + x);
                     fa_fence_after();
                     // O_x += P_x V: 8 steps of 16 keys, P from tensor memory (8 columns a step); then the next
                     // scores of this query tile, which overwrite P_x: the tensor pipe runs its products in order
@@ -393,7 +377,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                                   fa_desc_mnmajor(fa_smem(vt) + kk * 16 * 128, HALF_BYTES), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                     fa_commit(&pv_done[x]);
                     if (have_next) issue_s(x, j + 1);
-                    FA_ACC(7);
                 }
                 if (!ok) break;
                 fa_commit(&empty[(2 * j + 1) % FA_STAGES]);            // V(j) is no longer read
@@ -422,9 +405,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             bool alive = true;
             for (int j = 0; j < num_tiles && alive; ++j) {
                 const int k0 = kbegin + j * FA_BN;
-                FA_T0();
                 if (!fa_mbar_wait(&s_full[x], j & 1, (5u << 24) | (x << 20) | j, failed)) { alive = false; break; }
-                if (warp == 2) FA_ACC(8);
                 fa_fence_after();
                 const bool full_tile = rows_full && k0 + FA_BN - 1 <= xpos_first && k0 >= xlo_last && k0 + FA_BN <= kend;
                 const float mx = (full_tile ? fa_row_max<false>(tmem_s, k0, pos_r, lo_r, kend)
@@ -434,10 +415,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 float alpha = 1.0f;
                 if (mx > m_run + 8.0f) { alpha = fa_ex2(m_run - mx); m_run = mx; }     // m_run = -inf gives alpha 0
                 const float base = (m_run == -INFINITY) ? 0.0f : m_run;
-                if (warp == 2) FA_ACC(9);
                 // the previous P V of this query tile must be complete before O is rescaled and P is overwritten
                 if (j > 0 && !fa_mbar_wait(&pv_done[x], (j - 1) & 1, (6u << 24) | (x << 20) | j, failed)) { alive = false; break; }
-                if (warp == 2) FA_ACC(10);
                 fa_fence_after();
                 if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
@@ -449,14 +428,12 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                         fa_tmem_st32(tmem_o + c, o);
                     }
                 }
-                if (warp == 2) FA_ACC(11);
                 const float lsum = full_tile ? fa_row_probs<false>(tmem_s, p.scale_log2, base, k0, pos_r, lo_r, kend)
                                              : fa_row_probs<true>(tmem_s, p.scale_log2, base, k0, pos_r, lo_r, kend);
                 l_run = l_run * alpha + lsum;
                 fa_fence_before();
                 __syncwarp();
                 if (lane == 0) fa_mbar_arrive(&p_ready[x]);
-                if (warp == 2) FA_ACC(12);
             }
             // ---------------- output: O / l ----------------
             if (alive && num_tiles > 0 && fa_mbar_wait(&pv_done[x], (num_tiles - 1) & 1, (7u << 24) | (x << 20), failed)) {
@@ -511,23 +488,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 // in the layout attn_merge_kernel of attention_mma.cu combines.  Key ranges are those of the mma.sync decode
 // kernel: they depend on the request's own length only.
 // Needs a group of at most 16 query heads per kv head and pages of at most 64 keys.
-// Measured (Qwen3-8B sizes, 36 layers, CUDA-graph replays, against the mma.sync decode kernel): 3.15 ms a step
-// against 3.19 at batch 1, 3.97 against 4.15 at batch 8 (context 4096), 10.2 against 11.3 at batch 64, 9.3 against
-// 10.5 at batch 8 and 32k context, 16.2 against 18.3 at batch 64 and 8k context (5.7 TB/s over weights and cache).
-// A first version (query heads padded to 16 in every loop, butterfly shuffles for the column maxima, queries
-// loaded at the start of each item) was slower than the mma.sync kernel everywhere: its cycle counters
-// (-DFA_PROFILE) showed 3,500 cycles per tile in the softmax warps and 3,000 per item waiting for the queries.
-// Two further variants were measured in the same run and dropped: filling the rows of a partial tile from a spare
-// page instead of zeroing the ring at the start (4.04 against 4.00 ms at batch 8, 10.51 against 10.19 at batch 64),
-// and the sums of the probabilities by a product with a tile of ones instead of a reduction across threads at
-// the end of an item (no difference, and shorter key ranges were no faster with it).  Letting the SMs that a
-// small batch leaves without an item prefetch the output projection's weights into L2 meanwhile made the step
-// slower, not faster (4.12 against 4.04 ms at batch 8).  Two items at a time per CTA (a second group of four
-// softmax warps, the key tiles of the two items alternating through the ring, with the ring shared as it is or cut
-// into separate key and value stages) was correct but slower at every batch size (4.21 / 4.25 against 4.04 ms at
-// batch 8, 11.1 / 11.5 against 10.2 at batch 64): three stages of 64 KB are too few once two tiles are held by
-// softmax groups.  Separate key and value stages in the single-item kernel (keys free again right after S):
-// 10.69 against 10.42 ms at batch 64, 4.09 against 4.07 at batch 8 - twice the barrier traffic for nothing.
 // =============================================================================================================
 #define FD_THREADS 192
 #define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
@@ -695,9 +655,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
                 const unsigned bytes = (unsigned)__popc(mask) * page_bytes * HALVES * 2;
                 const int row = (page * p.nkv + w.kvh) * ps;
-                FA_T0();
                 if (use > 0 && !fa_mbar_wait(&empty[st], (use - 1) & 1, (1u << 24) | t, failed)) { ok = false; break; }
-                FA_ACC(0);
                 if (lane == 0) fa_mbar_expect_tx(&full[st], bytes);
                 __syncwarp();
                 if (page >= 0) {
@@ -721,9 +679,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             bool ok = true;
             auto issue_s = [&](int tt, int qbuf) -> bool {        // scores of tile tt into buffer tt & 1
                 const int st = tt % STAGES;
-                FA_T0();
                 if (!fa_mbar_wait(&full[st], (tt / STAGES) & 1, (2u << 24) | tt, failed)) return false;
-                FA_ACC(3);
                 fa_fence_after();
                 const unsigned char* kt = sKV + st * STAGE_BYTES;
                 const unsigned char* qt = sQ + qbuf * QBUF_BYTES;
@@ -737,18 +693,14 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 return true;
             };
             while (ok && !*failed && fd_next(p, it, w)) {
-                FA_T0();
                 if (!fa_mbar_wait(&q_ready[ic & 1], (ic >> 1) & 1, (3u << 24) | ic, failed)) break;
-                FA_ACC(4);
                 const int qbuf = ic & 1;
                 ++ic;
                 ok = issue_s(t, qbuf);
                 for (int j = 0; j < w.ntiles && ok; ++j, ++t) {
                     if (j + 1 < w.ntiles) ok = issue_s(t + 1, qbuf);      // the next scores while this tile is in its softmax
                     if (!ok) break;
-                    FA_T0();
                     if (!fa_mbar_wait(p_ready, t & 1, (4u << 24) | t, failed)) { ok = false; break; }
-                    FA_ACC(5);
                     fa_fence_after();
                     const int st = t % STAGES;
                     const unsigned char* vt = sKV + st * STAGE_BYTES + TILE_BYTES;
@@ -806,9 +758,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 #pragma unroll
             for (int g = 0; g < GP; ++g) { m_run[g] = -INFINITY; l_thr[g] = 0.0f; }
             for (int j = 0; j < w.ntiles; ++j, ++t) {
-                FA_T0();
                 alive = alive && fa_mbar_wait(&s_full[t & 1], (t >> 1) & 1, (5u << 24) | t, failed);
-                if (warp == 2) FA_ACC(8);
                 fa_fence_after();
                 float s[GP];
                 fa_tmem_ld_cols<GP>(tmem_base + (t & 1) * 16 + lane_base, s);
@@ -821,9 +771,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     const float wm = fa_warp_max(s[g]);
                     if (lane == 0) xm[g * 4 + quarter] = wm;
                 }
-                if (warp == 2) FA_ACC(9);
                 fd_softmax_sync();
-                if (warp == 2) FA_ACC(10);
                 float alpha[GP];
                 bool moved = false;
 #pragma unroll
@@ -837,10 +785,8 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     s[g] = fa_ex2(s[g] - base);                 // -inf gives 0
                     l_thr[g] = l_thr[g] * alpha[g] + s[g];
                 }
-                if (warp == 2) FA_ACC(11);
                 // the previous P V of this item must be complete before P is overwritten and O rescaled
                 if (j > 0) alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (6u << 24) | t, failed);
-                if (warp == 2) FA_ACC(12);
                 fa_fence_after();
                 {
                     unsigned char* pcol = sP + (tid >> 6) * PHALF_BYTES + ((tid & 7) << 1);
@@ -861,12 +807,9 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 __syncwarp();
                 if (lane == 0) fa_mbar_arrive(p_ready);
                 if (j == 0 && have_next) store_q((ic + 1) & 1);     // the next item's queries, fetched above
-                if (warp == 2) FA_ACC(13);
             }
             // ---------------- the item's result ----------------
-            FA_T0();
             alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (7u << 24) | t, failed);
-            if (warp == 2) FA_ACC(14);
             fa_fence_after();
             float o[GP];
             fa_tmem_ld_cols<GP>(tmem_base + O_COL + lane_base, o);
@@ -898,7 +841,6 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 }
             }
             fd_softmax_sync();            // xsum is read before the next item overwrites it
-            if (warp == 2) FA_ACC(15);
             w = wn; have = have_next; it = it_next; ++ic;
         }
     }
@@ -950,15 +892,6 @@ PI_EXPORT int pi_attention_tcgen05_status(unsigned* status) {
     }
     return 0;
 }
-
-#ifdef FA_PROFILE
-PI_EXPORT int pi_attention_tcgen05_profile(unsigned long long* out16) {
-    unsigned long long zero[16] = {0};
-    cudaMemcpyFromSymbol(out16, g_fa_prof, sizeof(zero));
-    cudaMemcpyToSymbol(g_fa_prof, zero, sizeof(zero));
-    return 0;
-}
-#endif
 
 PI_EXPORT int pi_attention_tcgen05_supported(int page_size) {
     return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;

@@ -10,11 +10,6 @@
 // Wide outputs (thousands of 16-feature tiles) use 8 warps per CTA with two register sets of weights in
 // flight; narrow ones (N = 4096 gives only 256 tiles) use 16 warps per CTA so that the whole GPU still has
 // loads in flight.
-// (Measured and dropped: splitting K further across the CTAs of a thread-block cluster, reduced through
-// distributed shared memory - the 33-100 MB products of a decode step got slower; applying the whole RMSNorm
-// inside the product from the 32-bit residual - every CTA then reads twice the activation bytes and does the
-// norm's arithmetic in its inner loop, 34 -> 52 us for the gate_up product; prefetching a CTA's whole tile into
-// L2 before the wait on the previous kernel - 8 % slower steps.)
 //
 // Within a 32-wide block of k, thread t of a quad supplies elements 8t..8t+7 of its row for both operands:
 // 8t+0..3 go to the four k slots that the thread owns in the first mma, 8t+4..7 to those of the second.  The
@@ -302,8 +297,10 @@ PI_EXPORT int pi_gemm_small_m_fused(const void* x, int ldx, const void* W, int l
     return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, 0, fu, stream);
 }
 
-// the plain product with the launch shape forced (for measurements)
+#ifdef PI_MEASURE_HOOKS
+// the plain product with the launch shape forced: only in builds made for measurements (-DPI_MEASURE_HOOKS)
 PI_EXPORT int pi_gemm_small_m_variant(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M,
                                       int N, int K, int variant, cudaStream_t stream) {
     return gemm_small_m_impl(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, variant, kPlain, stream);
 }
+#endif

@@ -180,7 +180,8 @@ __device__ T block_exclusive_scan(T v, T* sh /* 33 */, T* total) {
 __global__ void sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
                               const int* __restrict__ top_k, const float* __restrict__ top_p,
                               const unsigned long long* __restrict__ seeds,
-                              const unsigned long long* __restrict__ counters, int* __restrict__ out) {
+                              const unsigned long long* __restrict__ counters, int* __restrict__ out,
+                              const long long* __restrict__ row_entry) {
     __shared__ ArgMax sh_arg[33];
     __shared__ float sh_f[33];
     __shared__ int sh_i[33];
@@ -190,7 +191,11 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int voca
     const int row = blockIdx.x;
     const float* x = logits + (size_t)row * ld;
     const ArgMax top = block_argmax(x, vocab, sh_arg);
-    const float temp = temperature[row];
+    // Without row_entry the options of row r sit at index r.  With it, row_entry[2r] names the entry of the option
+    // tables that row r uses (tables filled once per set of options) and row_entry[2r + 1] is its draw counter.
+    const int entry = row_entry != nullptr ? (int)row_entry[2 * row] : row;
+    const unsigned long long counter = row_entry != nullptr ? (unsigned long long)row_entry[2 * row + 1] : counters[row];
+    const float temp = temperature[entry];
     if (temp <= 0.0f || top.i < 0) {
         if (threadIdx.x == 0) out[row] = top.i;
         return;
@@ -199,7 +204,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int voca
     const int c0 = threadIdx.x * chunk, c1 = min(vocab, c0 + chunk);
 
     // ---- top-k: the key of the k-th largest logit, and up to which index equal logits are kept ----------
-    const int k = top_k[row];
+    const int k = top_k[entry];
     unsigned key_k = 0u;       // keep keys > key_k, and keys == key_k with index <= tie_cut
     int tie_cut = INT_MAX;
     if (k > 0 && k < vocab) {
@@ -233,7 +238,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int voca
     const float inv_t = 1.0f / temp;
 
     // ---- top-p: the largest value v whose upper mass (logit >= v, inside the top-k set) reaches p * Z ---
-    const float pp = top_p[row];
+    const float pp = top_p[entry];
     unsigned key_p = 0u;
     if (pp > 0.0f && pp < 1.0f) {
         float z = 0.0f;
@@ -262,7 +267,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, int voca
     }
     float total;
     const float before = block_exclusive_scan<float>(mine, sh_f, &total);
-    const float target = uniform_from(seeds[row], counters[row]) * total;
+    const float target = uniform_from(seeds[entry], counter) * total;
     if (threadIdx.x == 0) sh_pick = INT_MAX;
     __syncthreads();
     int pick = INT_MAX;
@@ -298,8 +303,22 @@ PI_EXPORT int pi_sample(const float* logits, int ld, int rows, int vocab, const 
     if (vocab <= 0 || ld < vocab) return pi_refuse("pi_sample: vocab=%d ld=%d", vocab, ld);
     if (vocab > (1 << 24)) return pi_refuse("pi_sample: vocab=%d is beyond 2^24", vocab);
     pi_launch(sample_kernel, dim3(rows), dim3(vocab >= 4096 ? 1024 : 256), 0, stream, logits, ld, vocab, temperature, top_k,
-              top_p, seeds, counters, out);
+              top_p, seeds, counters, out, (const long long*)nullptr);
     return pi_check_launch("pi_sample");
+}
+
+// The same with the options in tables of `entries` entries that outlive the step: row r uses entry row_entry[2r]
+// and draw counter row_entry[2r + 1] (int64 pairs: the only per-step data, one small copy).
+PI_EXPORT int pi_sample_entries(const float* logits, int ld, int rows, int vocab, const float* temperature, const int* top_k,
+                                const float* top_p, const unsigned long long* seeds, const long long* row_entry,
+                                int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || ld < vocab) return pi_refuse("pi_sample_entries: vocab=%d ld=%d", vocab, ld);
+    if (vocab > (1 << 24)) return pi_refuse("pi_sample_entries: vocab=%d is beyond 2^24", vocab);
+    if (row_entry == nullptr) return pi_refuse("pi_sample_entries: the (entry, counter) pairs are missing");
+    pi_launch(sample_kernel, dim3(rows), dim3(vocab >= 4096 ? 1024 : 256), 0, stream, logits, ld, vocab, temperature, top_k,
+              top_p, seeds, (const unsigned long long*)nullptr, out, row_entry);
+    return pi_check_launch("pi_sample_entries");
 }
 
 // logits[rows[i], tokens[i]] = set ? values[i] : logits[...] + values[i]; (row, token) pairs must be distinct

@@ -34,14 +34,20 @@ def head_dims_of(model: DecoderModel) -> list:
     return sorted(dims)
 
 
+def page_bytes(model: DecoderModel, page_size: int, dtype: torch.dtype) -> int:
+    """Bytes that one page id costs: keys and values of ``page_size`` tokens in every cache of the model."""
+    item = torch.empty((), dtype=dtype).element_size()
+    return sum(2 * cs.num_kv_heads * cs.head_dim * page_size * item for cs in model.cache_specs() if cs is not None)
+
+
 def build_runner(model_dir: str | None = None, *, config=None, seed: int | None = None, dtype: str = "bfloat16",
                  device="cuda:0", page_size: int = 16, num_pages: int | None = None, max_tokens: int | None = None,
                  max_requests: int = 64, max_tokens_per_request: int | None = None,
                  max_tokens_per_step: int | None = None, attention_impl: str = "auto",
-                 use_cuda_graphs: bool = False, **spec_options) -> ModelRunner:
+                 use_cuda_graphs: bool = False, kv_bytes: int | None = None, **spec_options) -> ModelRunner:
     """From a model folder (``model_dir``) or from a configuration plus a seed (random weights on the
     device) to a ready step function.  The page pool holds ``num_pages`` pages per layer group, or
-    enough for ``max_tokens`` tokens (neither given: ``max_requests`` requests of the model's longest context,
+    as many as fit in ``kv_bytes`` bytes, or enough for ``max_tokens`` tokens (none given: ``max_requests`` requests of the model's longest context,
     at most 2^20 tokens)."""
     device = require_cuda(device)
     runtime = Runtime(device, dtype, attention_impl)
@@ -62,6 +68,10 @@ def build_runner(model_dir: str | None = None, *, config=None, seed: int | None 
         else:
             init_random_weights(model, 0 if seed is None else seed, runtime,
                                 "bfloat16" if runtime.mode == "bfloat16" else "float32")
+        if num_pages is None and kv_bytes is not None:
+            num_pages = int(kv_bytes) // page_bytes(model, page_size, runtime.act_dtype)
+            if num_pages <= 0:
+                raise ValueError(f"{kv_bytes} bytes hold no page of {page_size} tokens of this model")
         if num_pages is None:
             if max_tokens is None:
                 # every request slot at the model's longest context, capped at a million tokens

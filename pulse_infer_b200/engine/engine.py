@@ -52,6 +52,8 @@ class ContinuousBatchEngine:
         self.scheduler = ContinuousBatchScheduler(cache, max_batch_size, max_sequences or cache.max_slots, chunk_size,
                                                   max_tokens_per_step)
         self.last_batch: ScheduledBatch | None = None
+        # called as logits_hook(requests that sample in this step, float32 logits [len(requests), vocab]) before sampling
+        self.logits_hook = None
 
     def add_request(self, prompt_tokens, max_new_tokens: int, sampling: SamplingParams | None = None,
                     ignore_eos: bool = False) -> int:
@@ -132,6 +134,8 @@ class ContinuousBatchEngine:
         for req, n in entries:
             req.add_computed_tokens(n)
         if sampling_reqs:
+            if self.logits_hook is not None:
+                self.logits_hook(sampling_reqs, logits)
             history = None
             if any(r.sampling.presence_penalty > 0.0 for r in sampling_reqs):
                 history = [r.all_tokens() if r.sampling.presence_penalty > 0.0 else () for r in sampling_reqs]

@@ -20,19 +20,32 @@ import torch
 from .builder import build_runner
 from .context import Segment
 
-PAGE_SIZE = 16
+PAGE_SIZE = 16           # default page size in tokens
 TOKEN_ROUNDING = 64      # a request's token count is rounded up to this when sizing the pool
-MAX_LIVE_REQUESTS = 8
+MAX_LIVE_REQUESTS = 8    # default number of request slots
 
 
-def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, device="cuda:0", log=None) -> int:
-    """Run the steps read from ``lines`` (an iterable of JSON strings); returns the number of steps."""
+def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int | None, lines, device="cuda:0", log=None,
+           page_size: int = PAGE_SIZE, num_pages: int | None = None, max_requests: int = MAX_LIVE_REQUESTS) -> int:
+    """Run the steps read from ``lines`` (an iterable of JSON strings); returns the number of steps.
+    The pool holds ``num_pages`` pages of ``page_size`` tokens, or enough for ``max_tokens`` tokens (each request's
+    count rounded up to a multiple of 64 or of the page size, whichever is larger).  Beside the ``.f32`` files,
+    ``index.json`` lists for every row written: step, request, position of the token in its request, row."""
     os.makedirs(out_dir, exist_ok=True)
-    pool_tokens = (max_tokens + TOKEN_ROUNDING - 1) // TOKEN_ROUNDING * TOKEN_ROUNDING
-    runner = build_runner(model_dir, dtype=dtype, device=device, page_size=PAGE_SIZE, max_tokens=pool_tokens,
-                          max_requests=MAX_LIVE_REQUESTS, max_tokens_per_request=pool_tokens)
+    if page_size <= 0:
+        raise ValueError("page_size must be positive")
+    if num_pages is None:
+        if max_tokens is None:
+            raise ValueError("give max_tokens or num_pages")
+        rounding = max(TOKEN_ROUNDING, page_size)
+        pool_tokens = (max_tokens + rounding - 1) // rounding * rounding
+        num_pages = (pool_tokens + page_size - 1) // page_size
+    pool_tokens = num_pages * page_size
+    runner = build_runner(model_dir, dtype=dtype, device=device, page_size=page_size, num_pages=num_pages,
+                          max_requests=max_requests, max_tokens_per_request=pool_tokens)
     out = log or sys.stdout
     count = 0
+    index = []
     for line in lines:
         line = line.strip()
         if not line:
@@ -53,9 +66,16 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, dev
             if logits.shape[0] > 0:
                 arr = logits.detach().to("cpu", torch.float32).numpy().astype("<f4", copy=False)
                 arr.tofile(os.path.join(out_dir, f"{step_id}.f32"))
+                row = 0
+                for seg in segments:
+                    for w in seg.want:
+                        index.append({"step": step_id, "request": seg.request_id, "position": seg.start + w, "row": row})
+                        row += 1
         for rid in obj.get("end", []):
             if runner.cache.has(rid):
                 runner.close(rid)
         print(f"done {step_id}", file=out, flush=True)
         count += 1
+    with open(os.path.join(out_dir, "index.json"), "w", encoding="utf-8") as fh:
+        json.dump({"page_size": page_size, "num_pages": num_pages, "dtype": dtype, "rows": index}, fh)
     return count

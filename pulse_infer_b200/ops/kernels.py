@@ -638,6 +638,31 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     return out
 
 
+def sample_entries(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                   seeds: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """As ``sample``, with the options in tables that outlive the step: ``row_entry`` int64 [n, 2] gives, per row, the
+    table entry it uses and its draw counter."""
+    _need_cuda(logits, temperature, top_k, top_p, seeds, row_entry)
+    n, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(-1) != 1:
+        raise KernelError("logits must be float32 with unit stride")
+    if (temperature.dtype != torch.float32 or top_p.dtype != torch.float32 or top_k.dtype != torch.int32
+            or seeds.dtype != torch.int64 or row_entry.dtype != torch.int64):
+        raise KernelError("sampling tables: temperature/top_p float32, top_k int32, seeds int64; row_entry int64")
+    entries = temperature.numel()
+    for name, t in (("top_k", top_k), ("top_p", top_p), ("seeds", seeds)):
+        if t.numel() != entries or not t.is_contiguous():
+            raise KernelError(f"sampling table '{name}' must hold {entries} contiguous values")
+    if tuple(row_entry.shape) != (n, 2) or not row_entry.is_contiguous():
+        raise KernelError("row_entry must be contiguous int64 [rows, 2]")
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    lib = _lib("sampling")
+    _check(lib, lib.pi_sample_entries(_p(logits), c_int(logits.stride(0)), c_int(n), c_int(V), _p(temperature), _p(top_k),
+                                      _p(top_p), _p(seeds), _p(row_entry), _p(out), _stream()), "sample_entries")
+    return out
+
+
 def logit_edit(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, values: torch.Tensor, set_value: bool) -> None:
     """logits[rows[i], tokens[i]] += values[i] (or = values[i]); pairs must be distinct."""
     _need_cuda(logits, rows, tokens, values)

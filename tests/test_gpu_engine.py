@@ -267,8 +267,9 @@ def _trace_lines(reqs, plan):
     return "\n".join(lines) + "\n"
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(dtype, model_folders, plain_cache, tmp_path):
+@pytest.mark.parametrize("dtype, pool", [("float32", ["--max-tokens", "192"]), ("bfloat16", ["--max-tokens", "192"]),
+                                         ("bfloat16", ["--page-size", "8", "--num-pages", "23"])])
+def test_trace_run_program(dtype, pool, model_folders, plain_cache, tmp_path):
     """bin/trace_run as a user runs it: a subprocess, steps on standard input, logits in files."""
     need_gpu()
     folder, cfg = model_folders["B"], CONFIGS["B"]
@@ -278,7 +279,7 @@ def test_trace_run_program(dtype, model_folders, plain_cache, tmp_path):
             ([("a", 41, 70)], ["b"]), ([("c", 0, 64)], ["a"]), ([], ["c"])]
     out = tmp_path / "out"
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-                           "--out", str(out), "--max-tokens", "192"], input=_trace_lines(reqs, plan),
+                           "--out", str(out), *pool], input=_trace_lines(reqs, plan),
                           capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(len(plan))]
@@ -290,3 +291,15 @@ def test_trace_run_program(dtype, model_folders, plain_cache, tmp_path):
         got = np.fromfile(path, dtype="<f4").reshape(-1, cfg.vocab_size)
         want = np.concatenate([_plain(plain_cache, folder, reqs[rid])[a:b] for rid, a, b in entries])
         _check(got, want, dtype, f"trace step {step}")
+    # the index names every row: (step, request, position, row)
+    with open(out / "index.json") as fh:
+        index = json.load(fh)
+    assert index["page_size"] == (8 if "--page-size" in pool else 16)
+    rows = {(r["step"], r["row"]): (r["request"], r["position"]) for r in index["rows"]}
+    for step, (entries, _) in enumerate(plan):
+        row = 0
+        for rid, a, b in entries:
+            for pos in range(a, b):
+                assert rows[(step, row)] == (rid, pos)
+                row += 1
+    assert len(rows) == sum(b - a for entries, _ in plan for _, a, b in entries)

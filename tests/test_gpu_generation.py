@@ -155,6 +155,24 @@ def test_command_line_programs(model_folders, tmp_path):
     assert out.returncode == 0, out.stderr[-2000:]
     rec = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][0])
     assert len(rec["generated"]) == 5 and "tokens/s" in out.stdout
+    # the pool sized by memory, a token budget per step, and the largest logits behind every token (greedy: the first
+    # of them is the token, and they are the plain implementation's)
+    prompt = [5, 6, 7, 8, 9, 10, 11, 12, 13]
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen3_infer"), folder, "--dtype", "float32",
+                          "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "4", "--ignore-eos", "--greedy",
+                          "--presence-penalty", "0", "--kv-gb", "0.001", "--max-tokens-per-step", "4",
+                          "--print-logits-topk", "3"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rec = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][0])
+    want = _plain_generate(pc, pw, prompt, 4)
+    assert rec["generated"] == want and len(rec["logits_topk"]) == 4
+    toks = list(prompt)
+    for tok, top in zip(want, rec["logits_topk"]):
+        row = plain_model.forward(pc, pw, toks)[-1]
+        assert top[0][0] == tok and len(top) == 3
+        assert [t for t, _ in top] == [int(i) for i in np.argsort(-row, kind="stable")[:3]]
+        assert abs(top[0][1] - row[tok]) <= 2e-5 * np.abs(row).max() + 1e-5
+        toks.append(tok)
 
 
 # ---- each part of a layer alone ----------------------------------------------------------------------------
