@@ -326,6 +326,93 @@ def run_ours(args) -> dict:
     }
 
 
+WORKLOADS = {
+    # Qwen3-14B shape: a continuous batch of 32 requests, prompt lengths uniform in [128, 2048], 256 new tokens each
+    "serve14b": dict(shape=dict(num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                                head_dim=128, intermediate_size=17408, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                                tie_word_embeddings=False, max_position_embeddings=40960),
+                     requests=32, prompt_range=(128, 2048), new_tokens=256, max_batch=32),
+    # Qwen3-32B shape (q width 8192 != hidden): 16 requests reaching context 8192, prompts fed in portions beside the
+    # decode tokens of the requests that are already generating
+    "mixed32b": dict(shape=dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+                                head_dim=128, intermediate_size=25600, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                                tie_word_embeddings=False, max_position_embeddings=40960),
+                     requests=16, prompt_range=(7936, 7936), new_tokens=256, max_batch=16),
+}
+
+
+def run_workload(args) -> dict:
+    """A whole serving run through the Python entry point and the scheduler: requests in, generated ids out.
+    Reports the throughput, the mix of steps, and per kind of step the host time spent inside ``Engine.step()``
+    next to the GPU time of the step's kernels (CUDA events around each call)."""
+    import numpy as np
+    import torch
+    from pulse_infer_b200 import Engine
+    from pulse_infer_b200.config import Qwen3Config
+    w = WORKLOADS[args.workload]
+    shape = dict(w["shape"])
+    if args.layers:
+        shape["num_hidden_layers"] = args.layers
+    cfg = Qwen3Config(architecture="Qwen3ForCausalLM", torch_dtype="bfloat16", eos_token_ids=(), **shape)
+    rng = np.random.RandomState(0)
+    lo, hi = w["prompt_range"]
+    lengths = [int(rng.randint(lo, hi + 1)) for _ in range(w["requests"])]
+    prompts = [[int(t) for t in rng.randint(0, cfg.vocab_size, size=n)] for n in lengths]
+    pool_tokens = sum(n + w["new_tokens"] + PAGE for n in lengths)
+    t_build = time.time()
+    engine = Engine(None, config=cfg, seed=0, dtype="bfloat16", page_size=PAGE, max_tokens=pool_tokens,
+                    max_batch_size=w["max_batch"], chunk_size=args.chunk, max_tokens_per_step=args.budget,
+                    max_tokens_per_request=max(lengths) + w["new_tokens"] + PAGE, use_cuda_graphs=not args.no_graphs)
+    build_s = time.time() - t_build
+    # warm-up: one short request end to end (library start-up, first recordings), not timed
+    wid = engine.add_request(prompts[0][:64], 4, ignore_eos=True)
+    engine.run_until_complete()
+    assert len(engine.get_result(wid)) == 4
+    torch.cuda.synchronize()
+
+    ids = [engine.add_request(p, w["new_tokens"], ignore_eos=True) for p in prompts]
+    kinds, host_ms, events = [], [], []
+    clocks = ClockSampler()
+    clocks.start()
+    time.sleep(0.3)
+    c0 = time.monotonic()
+    t0 = time.perf_counter()
+    while engine.has_work():
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0 = time.perf_counter()
+        a.record()
+        engine.step()
+        b.record()
+        host_ms.append((time.perf_counter() - h0) * 1e3)
+        batch = engine.engine.last_batch
+        sizes = [n for _, n in batch.entries]
+        kinds.append("idle" if not sizes else "decode" if max(sizes) == 1 else "mixed" if min(sizes) == 1 else "prompt")
+        events.append((a, b))
+    torch.cuda.synchronize()
+    wall_s = time.perf_counter() - t0
+    clock_info = clocks.stop(c0, time.monotonic())
+    generated = sum(len(engine.get_result(i)) for i in ids)
+    assert generated == w["requests"] * w["new_tokens"]
+    gpu_ms = [a.elapsed_time(b) for a, b in events]
+    per_kind = {}
+    for kind in ("decode", "mixed", "prompt"):
+        idx = [i for i, k in enumerate(kinds) if k == kind]
+        if idx:
+            per_kind[kind] = {"steps": len(idx), "host_ms": round(sum(host_ms[i] for i in idx) / len(idx), 3),
+                              "gpu_ms": round(sum(gpu_ms[i] for i in idx) / len(idx), 3)}
+    st = engine.get_stats()
+    prompt_tokens = sum(lengths)
+    return {"workload": args.workload, "impl": "ours", "dtype": "bf16", "layers": cfg.num_hidden_layers,
+            "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "intermediate": cfg.intermediate_size, "requests": w["requests"], "prompt_tokens": prompt_tokens,
+            "prompt_range": [lo, hi], "new_tokens_each": w["new_tokens"], "chunk": args.chunk, "budget": args.budget,
+            "seconds": round(wall_s, 3), "generated_tokens_per_s": round(generated / wall_s, 1),
+            "all_tokens_per_s": round((generated + prompt_tokens) / wall_s, 1), "steps": len(kinds), "step_kinds": per_kind,
+            "gpu_busy_frac": round(sum(gpu_ms) / (wall_s * 1e3), 3), "preemptions": st.num_preemptions,
+            "weight_gb": round(engine.runner.model.weight_bytes() / 1e9, 2), "clocks": clock_info, "build_s": round(build_s, 1),
+            "data": "synthetic: seeded uniform-random token ids, seeded random weights"}
+
+
 def run_reference(args) -> dict:
     """The reference engine itself on the same shape, batch, context, steps and warm-up: ``baseline/_ref/ref_bench`` is
     the reference's unmodified sources built for sm_100 by ``baseline/build_reference.py`` plus a driver that calls its
@@ -406,6 +493,10 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=None, help="with --only: tokens of each prompt (default 2048)")
     ap.add_argument("--no-graphs", action="store_true", help="with --only: launch decode steps eagerly")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
+                    help="a whole serving run through Engine and the scheduler instead of the decode benchmark")
+    ap.add_argument("--chunk", type=int, default=512, help="with --workload: longest prompt portion of one request")
+    ap.add_argument("--budget", type=int, default=2048, help="with --workload: tokens of one step")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.gpus != 1:
@@ -418,6 +509,9 @@ def main() -> int:
         return 2
     if args.only:
         print(json.dumps(run_part(args)))
+        return 0
+    if args.workload:
+        print(json.dumps(run_workload(args)))
         return 0
     args.warmup = max(args.warmup, 3)
     result = run_ours(args)
