@@ -206,15 +206,20 @@ def timed_decode(engine, batch: int, steps: int, warmup: int, rng, through_api: 
     return ms, launches, mean_ctx, h2d, d2h
 
 
-def timed_prefill(engine, rng, repeats: int = 3, prompt: int | None = None):
+def timed_prefill(engine, rng, repeats: int = 3, prompt: int | None = None, cached: int = 0):
+    """Milliseconds of one step that feeds ``prompt`` tokens of one request (median of ``repeats`` after a warm-up);
+    ``cached``: tokens of that request already in the cache (fed before, untimed, in portions of 2,048)."""
     import torch
     from pulse_infer_b200.engine import Segment
     runner = engine.runner
     PROMPT = prompt or globals()["PROMPT"]
     tokens = [int(t) for t in rng.randint(0, engine.config.vocab_size, size=PROMPT)]
+    earlier = [int(t) for t in rng.randint(0, engine.config.vocab_size, size=cached)]
     times = []
     for i in range(repeats + 1):
         runner.open(("prefill", i))
+        for at in range(0, cached, 2048):
+            runner.step([Segment(("prefill", i), earlier[at:at + 2048], [])])
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         if i == repeats:
@@ -248,10 +253,12 @@ def run_part(args) -> dict:
     rng = np.random.RandomState(0)
     if args.only == "prefill":
         T = args.prompt_len or PROMPT
-        engine = make_engine(cfg, args.batch, graphs=not args.no_graphs, context=max(CONTEXT, T), prompt=T)
-        ms = timed_prefill(engine, rng, repeats=max(1, args.steps), prompt=T)
-        return {"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": T, "ms": round(ms, 3),
-                "tokens_per_s": round(T / ms * 1e3, 1)}
+        engine = make_engine(cfg, args.batch, graphs=not args.no_graphs, context=max(CONTEXT, T + args.cached), prompt=max(T, 2048))
+        ms = timed_prefill(engine, rng, repeats=max(1, args.steps), prompt=T, cached=args.cached)
+        peaks, _ = load_peaks()
+        flops = prefill_flops(cfg, T) + 4.0 * cfg.num_attention_heads * cfg.head_dim * T * args.cached * cfg.num_hidden_layers
+        return {"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": T, "cached": args.cached, "ms": round(ms, 3),
+                "tokens_per_s": round(T / ms * 1e3, 1), "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
     prompt = args.prompt_len or min(PROMPT, args.context - args.steps - args.warmup - 1)
     engine = make_engine(cfg, args.batch, graphs=not args.no_graphs, context=args.context, prompt=prompt)
     ms, launches, ctx, _, _ = timed_decode(engine, args.batch, args.steps, args.warmup, rng, False, context=args.context,
@@ -491,6 +498,7 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None, help="run one phase only (for profilers)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: the context the timed steps end at")
     ap.add_argument("--prompt-len", type=int, default=None, help="with --only: tokens of each prompt (default 2048)")
+    ap.add_argument("--cached", type=int, default=0, help="with --only prefill: tokens of the request already in the cache")
     ap.add_argument("--no-graphs", action="store_true", help="with --only: launch decode steps eagerly")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,

@@ -18,7 +18,7 @@ from .sampling import Sampler, SamplingParams
 class Engine:
     def __init__(self, model: str | None = None, *, config=None, seed: int | None = None, dtype: str = "bfloat16",
                  device: str = "cuda:0", page_size: int = 16, num_pages: int | None = None,
-                 max_tokens: int | None = None, max_batch_size: int = 8, chunk_size: int = 256,
+                 max_tokens: int | None = None, max_batch_size: int = 8, chunk_size: int = 1024,
                  max_tokens_per_step: int | None = None, max_tokens_per_request: int | None = None,
                  use_cuda_graphs: bool = True, attention_impl: str = "auto", rope_pairing: str | None = None,
                  lookahead: bool | None = None, kv_bytes: int | None = None):
@@ -26,6 +26,10 @@ class Engine:
         The page pool is ``num_pages`` pages of ``page_size`` tokens, or what fits in ``kv_bytes`` bytes, or enough
         for ``max_tokens`` tokens
         (default: ``max_batch_size`` requests of the model's longest context, capped at 1M tokens).
+        ``chunk_size`` (longest prompt portion of one request in one step) defaults to 1,024 and ``max_tokens_per_step``
+        to 2,048 (or ``chunk_size`` if that is larger): on a B200 a step of 128 or 256 prompt tokens costs as much as
+        one of 512 (the weights are read either way), and 1,024-token portions reach the prompt throughput of whole
+        prompts, while a step stays short enough for the decoding requests that ride along.
         ``lookahead`` (default: on with CUDA graphs): a decode step stays in flight when ``step()`` returns and its
         tokens are read while the next one runs; ``step()`` then returns the tokens of the step before."""
         spec_options = {} if rope_pairing is None else {"rope_pairing": rope_pairing}
@@ -38,7 +42,7 @@ class Engine:
         self.sampler = Sampler(self.runner.runtime.device)
         self.engine = ContinuousBatchEngine(self.runner, self.sampler, getattr(self.config, "eos_token_ids", ()),
                                             max_batch_size=max_batch_size, chunk_size=chunk_size,
-                                            max_tokens_per_step=max_tokens_per_step,
+                                            max_tokens_per_step=max_tokens_per_step or max(2048, chunk_size),
                                             lookahead=use_cuda_graphs if lookahead is None else lookahead)
 
     # ---- the reference engine's calls ------------------------------------------------------------------

@@ -55,6 +55,11 @@ struct FaParams {
     int page_size, window;
     float scale_log2;
     int tiles_per_seg, num_segments;
+    // key splitting for short portions behind long contexts: gridDim.y CTAs share the key tiles of a query block and
+    // leave (reference point of the exponentials, sum, unnormalised output) per row for attn_prompt_merge_kernel
+    int splits;
+    float* part_acc;       // [tokens * nq][splits][D]
+    float* part_ml;        // [tokens * nq][splits][2]
 };
 
 // ---- PTX wrappers (see gemm_tcgen05.cu for the same set with comments) ------------------------------------
@@ -253,9 +258,28 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int* table = p.block_table + (size_t)p.seg_slot[seg] * p.bt_stride;
     const int row_last = min(row0 + FA_ROWS, rows_total) - 1;
     const int pos_first = start + row0 / G, pos_last = start + row_last / G;
-    const int kbegin = (fa_window_lo(pos_first, p.window) / FA_BN) * FA_BN;
+    int kbegin = (fa_window_lo(pos_first, p.window) / FA_BN) * FA_BN;
     const int kend = pos_last + 1;
-    const int num_tiles = (kend - kbegin + FA_BN - 1) / FA_BN;
+    int num_tiles = (kend - kbegin + FA_BN - 1) / FA_BN;
+    const int split = blockIdx.y;
+    if (p.splits > 1) {
+        // this CTA's share of the key tiles (contiguous, as even as it goes); a share may be empty
+        const int t0 = (int)((long long)split * num_tiles / p.splits), t1 = (int)((long long)(split + 1) * num_tiles / p.splits);
+        kbegin += t0 * FA_BN;
+        num_tiles = t1 - t0;
+        if (num_tiles <= 0) {
+            pdl_wait();
+            for (int r = threadIdx.x; r < FA_ROWS; r += FA_THREADS) {
+                const int rf = row0 + r;
+                if (rf < rows_total) {
+                    const size_t orow = (size_t)(tok_off + rf / G) * p.nq + kvh * G + rf % G;
+                    p.part_ml[(orow * p.splits + split) * 2] = -INFINITY;
+                    p.part_ml[(orow * p.splits + split) * 2 + 1] = 0.0f;
+                }
+            }
+            return;
+        }
+    }
 
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -438,6 +462,24 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             // ---------------- output: O / l ----------------
             if (alive && num_tiles > 0 && fa_mbar_wait(&pv_done[x], (num_tiles - 1) & 1, (7u << 24) | (x << 20), failed)) {
                 fa_fence_after();
+                if (p.splits > 1) {
+                    // a share of the keys: the merge kernel divides by the sum of all shares
+                    const size_t orow_i = row_valid ? (size_t)(tok_off + rf / G) * p.nq + kvh * G + rf % G : 0;
+                    if (row_valid) {
+                        p.part_ml[(orow_i * p.splits + split) * 2] = l_run > 0.0f ? m_run : -INFINITY;
+                        p.part_ml[(orow_i * p.splits + split) * 2 + 1] = l_run;
+                    }
+                    float* acc = p.part_acc + (orow_i * p.splits + split) * D;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        float o[32];
+                        fa_tmem_ld32(tmem_o + c, o);           // the whole warp loads; only rows that exist store
+                        if (row_valid) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(acc + c + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                        }
+                    }
+                } else {
                 const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
                 bf16* orow = p.out + (size_t)(tok_off + (row_valid ? rf / G : 0)) * p.nq * D + (size_t)(kvh * G + (row_valid ? rf % G : 0)) * D;
 #pragma unroll 1
@@ -458,6 +500,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                         }
                     }
                 }
+                }
             }
         }
     }
@@ -468,6 +511,38 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         __syncwarp();
         fa_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Combine the shares of the keys that attn_tcgen05_kernel left for the rows of prompt portions: one block per
+// (token, head), one thread per element of the head.  out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s, the shares
+// taken in order; a share that saw no key (l = 0) is skipped.
+template <int D>
+__global__ void attn_prompt_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int splits,
+                                         bf16* __restrict__ out, const int* __restrict__ token_seg,
+                                         const int* __restrict__ seg_len, int nq) {
+    pdl_wait();
+    pdl_trigger();
+    const int row = blockIdx.x, t = row / nq;
+    if (seg_len[token_seg[t]] == 1) return;          // single tokens are the decode kernel's
+    const float2* ml = reinterpret_cast<const float2*>(part_ml + (size_t)row * splits * 2);
+    const float* acc = part_acc + (size_t)row * splits * D;
+    float mstar = -INFINITY;
+    for (int s = 0; s < splits; ++s) {
+        const float2 v = ml[s];
+        if (v.y > 0.0f) mstar = fmaxf(mstar, v.x);
+    }
+    for (int e = threadIdx.x; e < D; e += blockDim.x) {
+        float num = 0.0f, den = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float2 v = ml[s];
+            if (v.y > 0.0f) {
+                const float w = fa_ex2(v.x - mstar);
+                num += w * acc[(size_t)s * D + e];
+                den += w * v.y;
+            }
+        }
+        out[(size_t)row * D + e] = __float2bfloat16_rn(den > 0.0f ? num / den : 0.0f);
     }
 }
 
@@ -901,8 +976,12 @@ PI_EXPORT int pi_attention_tcgen05_supported(int page_size) {
 PI_EXPORT int pi_attention_tcgen05(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
                                    const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
                                    const int* seg_start, const int* seg_len, void* out, int num_segments, int max_seg_len,
-                                   int nq, int nkv, int page_size, int window, float scale, cudaStream_t stream) {
+                                   int nq, int nkv, int page_size, int window, float scale, int splits, float* part_acc,
+                                   float* part_ml, const int* token_seg, int num_tokens, cudaStream_t stream) {
     if (num_segments <= 0 || max_seg_len <= 0) return 0;
+    if (splits < 1 || splits > 64) return pi_refuse("pi_attention_tcgen05: splits=%d must be 1..64", splits);
+    if (splits > 1 && (part_acc == nullptr || part_ml == nullptr || token_seg == nullptr || num_tokens <= 0))
+        return pi_refuse("pi_attention_tcgen05: key splitting needs its scratch, the token-to-segment table and the token count");
     if (!(scale > 0.0f)) return pi_refuse("pi_attention_tcgen05: the score scale must be positive");
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return pi_refuse("pi_attention_tcgen05: nq=%d must be a positive multiple of nkv=%d", nq, nkv);
     if (!pi_attention_tcgen05_supported(page_size)) return pi_refuse("pi_attention_tcgen05: page size %d is not one of 8, 16, 32, 64, 128", page_size);
@@ -921,6 +1000,7 @@ PI_EXPORT int pi_attention_tcgen05(const void* q, int q_stride, const void* kcac
     p.scale_log2 = scale * 1.4426950408889634f;
     p.tiles_per_seg = (int)(((long long)max_seg_len * p.group + FA_ROWS - 1) / FA_ROWS);
     p.num_segments = num_segments;
+    p.splits = splits; p.part_acc = part_acc; p.part_ml = part_ml;
     const long long ctas = (long long)num_segments * p.tiles_per_seg * nkv;
     if (ctas > 2147483647LL) return pi_refuse("pi_attention_tcgen05: %lld tiles are beyond the grid limit", ctas);
     static bool configured = false;
@@ -935,8 +1015,12 @@ PI_EXPORT int pi_attention_tcgen05(const void* q, int q_stride, const void* kcac
         }
         configured = true;
     }
-    pi_launch(kernel, dim3((unsigned)ctas), dim3(FA_THREADS), smem, stream, mk, mv, p);
-    return pi_check_launch("pi_attention_tcgen05");
+    pi_launch(kernel, dim3((unsigned)ctas, (unsigned)splits), dim3(FA_THREADS), smem, stream, mk, mv, p);
+    rc = pi_check_launch("pi_attention_tcgen05");
+    if (rc || splits == 1) return rc;
+    pi_launch(attn_prompt_merge_kernel<PI_HEAD_DIM>, dim3((unsigned)((long long)num_tokens * nq)), dim3(PI_HEAD_DIM), 0, stream,
+              (const float*)part_acc, (const float*)part_ml, splits, (bf16*)out, token_seg, seg_len, nq);
+    return pi_check_launch("pi_attention_tcgen05 merge");
 }
 
 

@@ -49,6 +49,10 @@ class AttentionScratch:
     acc: torch.Tensor | None
     ml: torch.Tensor | None
     split_keys: int = ops.SPLIT_KEYS
+    # key splitting of the prompt kernel (short portions behind long contexts): shares per query block and their scratch
+    prompt_splits: int = 1
+    prompt_acc: torch.Tensor | None = None
+    prompt_ml: torch.Tensor | None = None
 
 
 class StepContext:
@@ -188,5 +192,14 @@ class StepContext:
                     sc = AttentionScratch(splits, acc, ml, split_keys)
                 else:
                     sc = AttentionScratch(1, None, None, split_keys)
+            if self.has_prompt and ops.attention_tcgen05_usable(head_dim, self.cache_manager.page_size) \
+                    and self.act_dtype == torch.bfloat16:
+                portions = [(s.start, len(s.tokens)) for s in self.segments if len(s.tokens) > 1]
+                shares = ops.choose_prompt_splits(portions, num_heads // max(num_kv_heads, 1), num_kv_heads, window)
+                if shares > 1:
+                    rows = self.num_tokens * num_heads
+                    sc.prompt_splits = shares
+                    sc.prompt_acc = torch.empty((rows, shares, head_dim), dtype=torch.float32, device=self.device)
+                    sc.prompt_ml = torch.empty((rows, shares, 2), dtype=torch.float32, device=self.device)
             self._scratch[key] = sc
         return sc

@@ -312,21 +312,50 @@ def attention_tcgen05_usable(head_dim: int, page_size: int) -> bool:
     return TCGEN05_ATTENTION and head_dim in (64, 128) and page_size in (8, 16, 32, 64, 128)
 
 
+def choose_prompt_splits(portions, group: int, num_kv_heads: int, window: int | None) -> int:
+    """How many CTAs share the key tiles of a query block in the prompt attention kernel.  ``portions``: (start, length)
+    of the step's segments of more than one token.  A query block is 256 rows (tokens x heads of a group); a step with
+    few of them behind a long context - a short portion of a long prompt - would leave most SMs idle while a few walk
+    thousands of keys, so their keys are cut into shares.  1 when the blocks fill the GPU or the contexts are short."""
+    forced = os.environ.get("PULSE_PROMPT_SPLITS")
+    if forced:
+        return max(1, int(forced))
+    if not portions:
+        return 1
+    ctas = sum((n * group + 255) // 256 for _, n in portions) * max(num_kv_heads, 1)
+    keys = max((min(start + n, (window or (start + n)) + n)) for start, n in portions)
+    tiles = (keys + 127) // 128
+    sms = sm_count()
+    if ctas * 2 > sms or tiles < 8:
+        return 1
+    return max(1, min(sms // ctas, tiles // 4, 16))
+
+
 def attention_tcgen05(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len,
                       num_tokens: int, num_segments: int, max_seg_len: int, nq: int, nkv: int, head_dim: int,
-                      page_size: int, window: int | None, scale: float, out: torch.Tensor) -> torch.Tensor:
+                      page_size: int, window: int | None, scale: float, out: torch.Tensor, splits: int = 1,
+                      part_acc: torch.Tensor | None = None, part_ml: torch.Tensor | None = None,
+                      token_seg: torch.Tensor | None = None) -> torch.Tensor:
     """Prompt portions (segments of more than one token) on tcgen05 tensor cores; rows of single-token
-    segments in ``out`` are left untouched (see csrc/attention_tcgen05.cu)."""
-    _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, out)
+    segments in ``out`` are left untouched (see csrc/attention_tcgen05.cu).  ``splits`` > 1: that many CTAs share the
+    key tiles of every query block and a second kernel combines their shares; needs float32 scratch ``part_acc``
+    [tokens * nq * splits * head_dim], ``part_ml`` [tokens * nq * splits * 2] and ``token_seg`` (int32 [tokens])."""
+    _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, out, part_acc, part_ml, token_seg)
     _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
     if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
         raise KernelError("the tcgen05 attention kernel takes bfloat16 only")
+    if splits > 1:
+        need = num_tokens * nq * splits
+        if (part_acc is None or part_ml is None or token_seg is None or part_acc.numel() < need * head_dim
+                or part_ml.numel() < need * 2 or part_acc.dtype != torch.float32 or part_ml.dtype != torch.float32):
+            raise KernelError("scratch for the split prompt attention is missing or too small")
     lib = _lib("attention_tcgen05", head_dim)
     _check(lib, lib.pi_attention_tcgen05(
         _p(q), c_int(q_stride), _p(kcache), _p(vcache), ctypes.c_longlong(kcache.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), c_int(num_segments),
-        c_int(max_seg_len), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale), _stream()),
-        "attention_tcgen05")
+        c_int(max_seg_len), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0), c_float(scale), c_int(splits),
+        _p(part_acc), _p(part_ml), _p(token_seg), c_int(num_tokens), _stream()),
+        "attention_tcgen05", launches=2 if splits > 1 else 1)
     return out
 
 
@@ -352,12 +381,14 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
                   max_splits: int, part_acc, part_ml, nq: int, nkv: int, head_dim: int, page_size: int,
                   window: int | None, scale: float, out: torch.Tensor | None = None,
                   split_keys: int = SPLIT_KEYS, prefetch: torch.Tensor | None = None,
-                  prompt_on_tcgen05: bool = True, decode_on_tcgen05: bool | None = None) -> torch.Tensor:
+                  prompt_on_tcgen05: bool = True, decode_on_tcgen05: bool | None = None, prompt_splits: int = 1,
+                  prompt_acc: torch.Tensor | None = None, prompt_ml: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core paged attention for bfloat16 over request segments.  Prompt portions (segments of several tokens)
     and single tokens are separate kernels: for head sizes 64 / 128 the tcgen05 kernels of csrc/attention_tcgen05.cu
     (``prompt_on_tcgen05`` / ``decode_on_tcgen05``; the ranges of a split decode are combined by the merge kernel
     of csrc/attention_mma.cu), otherwise - and for sizes those do not take - the mma.sync kernels of
-    csrc/attention_mma.cu."""
+    csrc/attention_mma.cu.  ``prompt_splits`` / ``prompt_acc`` / ``prompt_ml``: key splitting of the tcgen05 prompt
+    kernel (see ``attention_tcgen05``)."""
     _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml)
     _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
     if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
@@ -369,7 +400,8 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
     if has_prompt and prompt_on_tcgen05 and attention_tcgen05_usable(head_dim, page_size):
         # prompt portions on the tcgen05 kernel, single tokens (if any) on the decode kernel below
         attention_tcgen05(q, q_stride, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, num_tokens,
-                          num_segments, max_seg_len, nq, nkv, head_dim, page_size, window, scale, out)
+                          num_segments, max_seg_len, nq, nkv, head_dim, page_size, window, scale, out,
+                          splits=prompt_splits, part_acc=prompt_acc, part_ml=prompt_ml, token_seg=token_seg)
         if not has_decode:
             return out
         has_prompt = False

@@ -109,7 +109,8 @@ class Attention(Mixer):
                 ctx.seg_len, ctx.token_seg, ctx.num_tokens, ctx.num_segments, ctx.max_seg_len, ctx.has_prompt,
                 ctx.has_decode, scratch.max_splits, scratch.acc, scratch.ml, self.num_heads, self.num_kv_heads,
                 self.head_dim, cache.page_size, self.window, self.scale, split_keys=scratch.split_keys,
-                prefetch=ctx.prefetch(getattr(ctx, "upcoming_weights", None)))
+                prefetch=ctx.prefetch(getattr(ctx, "upcoming_weights", None)), prompt_splits=scratch.prompt_splits,
+                prompt_acc=scratch.prompt_acc, prompt_ml=scratch.prompt_ml)
         else:
             attn = ops.attention_simple(
                 qkv, q_stride, cache.keys, cache.values, cache.block_table, ctx.token_slot, ctx.positions,

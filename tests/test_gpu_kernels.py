@@ -136,7 +136,7 @@ def test_qk_norm_rope_write(dtype, nq, nkv, d, rot, adjacent, page):
     assert int(err.item()) == 2 * nkv
 
 
-def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengths, seed=0, spike=None):
+def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengths, seed=0, spike=None, prompt_splits=1):
     """segs: (slot, start, n) with start + n <= lengths[slot]; queries random; returns max error / scale."""
     kv = PagedKV(lengths, nkv, d, page, dtype, dev, seed=seed)
     meta = segments_to_device(segs, dev)
@@ -163,10 +163,14 @@ def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengt
         splits = ops.attention_num_splits(dec_pos, window) if any(n == 1 for n in lens) else 1
         acc = torch.empty(T * nq * splits * d, dtype=torch.float32, device=dev)
         ml = torch.empty(T * nq * splits * 2, dtype=torch.float32, device=dev)
+        # scratch of the split prompt kernel starts as NaN: a share that is read without having been written shows
+        pacc = torch.full((T * nq * prompt_splits * d,), float("nan"), dtype=torch.float32, device=dev) if prompt_splits > 1 else None
+        pml = torch.full((T * nq * prompt_splits * 2,), float("nan"), dtype=torch.float32, device=dev) if prompt_splits > 1 else None
         out = ops.attention_mma(qflat, nq * d, kv.kcache, kv.vcache, kv.table_dev, meta["seg_off"], meta["seg_slot"],
                                 meta["seg_start"], meta["seg_len"], meta["token_seg"], T, len(segs), max(lens),
                                 any(n > 1 for n in lens), any(n == 1 for n in lens), splits, acc, ml, nq, nkv, d, page,
-                                window, scale, prompt_on_tcgen05=(impl == "tcgen05"), decode_on_tcgen05=(impl == "tcgen05"))
+                                window, scale, prompt_on_tcgen05=(impl == "tcgen05"), decode_on_tcgen05=(impl == "tcgen05"),
+                                prompt_splits=prompt_splits, prompt_acc=pacc, prompt_ml=pml)
         if impl == "tcgen05":
             if not ops.attention_tcgen05_usable(d, page):
                 pytest.skip("the tcgen05 kernel takes head sizes 64 / 128 and page sizes 8..128")
@@ -263,6 +267,33 @@ def test_attention_tcgen05_long_portions(nq, nkv, d, page, window):
     segs = [(0, 100, 600), (1, 0, 131), (2, 517, 512), (3, 39, 1)]
     err = _attention_case(ops, dev, torch.bfloat16, "tcgen05", nq, nkv, d, page, window, segs, lengths, seed=nq + page)
     assert err < 0.03
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 8), (4, 1, 64, 128), (32, 8, 128, 16)])
+@pytest.mark.parametrize("window", [None, 130, 900])
+@pytest.mark.parametrize("shares", [2, 3, 7, 16])
+def test_attention_tcgen05_portions_with_shared_keys(nq, nkv, d, page, window, shares):
+    """Short portions behind long contexts with the key tiles of every query block cut into shares (2 to 16 CTAs a
+    block; with 16 some shares of the short contexts are empty), combined by the merge kernel; a single token beside
+    them is untouched by it.  One key far back is made to stand out, so a share that is dropped or counted twice shows."""
+    dev, ops = need_gpu(), _ops()
+    lengths = [2300, 131, 1500, 40]
+    segs = [(0, 2200, 100), (1, 0, 131), (2, 1400, 40), (3, 39, 1)]
+    err = _attention_case(ops, dev, torch.bfloat16, "tcgen05", nq, nkv, d, page, window, segs, lengths, seed=nq + shares,
+                          spike=(0, 5, nq - 1) if window is None else (0, 2300 - window + 3, nq - 1), prompt_splits=shares)
+    assert err < 0.03
+
+
+def test_prompt_shares_are_chosen_from_the_step():
+    """CPU arithmetic of ``choose_prompt_splits``: shares only when the query blocks leave SMs idle and contexts are long."""
+    ops = _ops()
+    sms = ops.kernels.sm_count()
+    assert ops.choose_prompt_splits([], 4, 8, None) == 1
+    assert ops.choose_prompt_splits([(0, 2048)], 4, 8, None) == 1                    # 256 blocks: the GPU is full
+    assert ops.choose_prompt_splits([(100, 128)], 4, 8, None) == 1                   # two key tiles: nothing to share
+    few = ops.choose_prompt_splits([(16384, 128)], 4, 8, None)                       # 16 CTAs walking 129 key tiles
+    assert few == min(sms // 16, 16)
+    assert ops.choose_prompt_splits([(16384, 128)], 4, 8, 1024) == min(sms // 16, (1152 + 127) // 128 // 4, 16)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 515, 96), (33, 515, 100), (64, 64, 16), (130, 77, 1000), (7, 4096, 4096)])
