@@ -572,6 +572,16 @@ struct FdParams {
     const int* block_table; int bt_stride;
     const int* seg_off; const int* seg_slot; const int* seg_start; const int* seg_len;
     bf16* out; float* part_acc; float* part_ml; int max_splits;
+    // fuse = 1: q holds the raw q/k/v projections of the step's tokens [T, (nq + 2 nkv) D].  The kernel then does what
+    // qk_norm_rope_write_kernel (elementwise.cu) does for single tokens: the queries of an item are normalised per head
+    // and rotated as they are loaded; the item that holds a request's newest position normalises and rotates that
+    // token's key, writes it and the value into their page, and only then requests the tile that contains it.
+    int fuse;
+    bf16* kpool; bf16* vpool;            // [pages][nkv][page_size][D]
+    const void* qw; const void* kw;      // per-head norm weights [D] (bf16, or float if w_f32); null: no norm
+    int w_f32; float eps;
+    const float* cos_t; const float* sin_t; int rot_pairs;   // [T][rot_pairs]; adjacent pairs (2i, 2i + 1); null: no rotation
+    int* error_count;                    // tokens whose page is missing are counted here, not written
     int nq, nkv, group;
     int page_size, window;
     float scale_log2;
@@ -656,6 +666,62 @@ __device__ __forceinline__ bool fd_next(const FdParams& p, int& it, FdItem& w) {
     return false;
 }
 
+__device__ __forceinline__ float fd_weight(const void* w, int w_f32, int i) {
+    return w_f32 ? reinterpret_cast<const float*>(w)[i] : __bfloat162float(reinterpret_cast<const bf16*>(w)[i]);
+}
+
+// The newest token of item w's request: its key (normalised, rotated) and value go into their page.  One warp; lane
+// takes four elements (two adjacent pairs), the arithmetic of qk_norm_rope_write_kernel in the same order.
+template <int D>
+__device__ __forceinline__ void fd_write_new_token(const FdParams& p, const FdItem& w, const int* table, int lane) {
+    const int tok = p.seg_off[w.seg];
+    const int page = table[w.pos / p.page_size];
+    if (page < 0) {
+        if (lane == 0) atomicAdd(p.error_count, 1);
+        return;
+    }
+    const size_t dst = (((size_t)page * p.nkv + w.kvh) * p.page_size + (w.pos % p.page_size)) * D;
+    const bf16* krow = p.q + (size_t)tok * p.q_stride + (size_t)(p.nq + w.kvh) * D;
+    const bf16* vrow = krow + (size_t)p.nkv * D;
+    const bool mine = lane < D / 4;
+    if (mine) reinterpret_cast<uint2*>(p.vpool + dst)[lane] = reinterpret_cast<const uint2*>(vrow)[lane];
+    float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float ss = 0.0f;
+    if (mine) {
+        const uint2 raw = reinterpret_cast<const uint2*>(krow)[lane];
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+        ss += x[0] * x[0] + x[1] * x[1];
+        ss += x[2] * x[2] + x[3] * x[3];
+    }
+    float inv = 1.0f;
+    if (p.kw != nullptr) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        inv = 1.0f / sqrtf(ss / (float)D + p.eps);
+    }
+    if (mine) {
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = p.kw != nullptr ? x[i] * inv * fd_weight(p.kw, p.w_f32, 4 * lane + i) : x[i];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int pr = 2 * lane + h;
+            if (p.cos_t != nullptr && pr < p.rot_pairs) {
+                const float c = p.cos_t[(size_t)tok * p.rot_pairs + pr], sn = p.sin_t[(size_t)tok * p.rot_pairs + pr];
+                const float r0 = v[2 * h] * c - v[2 * h + 1] * sn;
+                const float r1 = v[2 * h] * sn + v[2 * h + 1] * c;
+                v[2 * h] = r0; v[2 * h + 1] = r1;
+            }
+        }
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const unsigned*>(&a); raw.y = *reinterpret_cast<const unsigned*>(&b);
+        reinterpret_cast<uint2*>(p.kpool + dst)[lane] = raw;
+    }
+}
+
 // GP: the group's query heads rounded up to 4, 8 or 16
 template <int D, int GP>
 __global__ void __launch_bounds__(FD_THREADS, 1)
@@ -725,6 +791,13 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             const int* table = p.block_table + (size_t)p.seg_slot[w.seg] * p.bt_stride;
             for (int j = 0; j < w.ntiles; ++j, ++t) {
                 const int st = t % STAGES, use = t / STAGES;
+                if (p.fuse && j == w.ntiles - 1 && w.split == w.nsplits - 1) {
+                    // the tile about to be requested holds the newest position: its key and value are written first,
+                    // by this warp, and made visible to the TMA unit (proxy fence by the writers, then the warp meets)
+                    fd_write_new_token<D>(p, w, table, lane);
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    __syncwarp();
+                }
                 const int key = w.kb + j * FA_BN + lane * ps;
                 const int page = (lane < pages_per_tile && key < w.ke) ? table[key / ps] : -1;
                 const unsigned mask = __ballot_sync(0xffffffffu, page >= 0);
@@ -807,6 +880,50 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     qv[c] = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.q_stride + (size_t)(w.kvh * G + idx / (D / 8)) * D + (idx % (D / 8)) * 8);
             }
         };
+        // fused mode: the raw queries become normalised, rotated ones.  A head's D elements sit in D / 8 neighbouring
+        // threads (8 elements each); threads beyond the group's heads hold zeros and only take part in the shuffles.
+        auto finish_q = [&](const FdItem& w) {
+            if (!p.fuse) return;
+            const int tok = p.seg_off[w.seg];
+#pragma unroll
+            for (int c = 0; c < QCHUNKS; ++c) {
+                const int idx = tid + c * 128;
+                const int ch = idx % (D / 8);
+                float x[8];
+                {
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&qv[c]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { x[2 * i] = __low2float(h2[i]); x[2 * i + 1] = __high2float(h2[i]); }
+                }
+                float inv = 1.0f;
+                if (p.qw != nullptr) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+                    for (int o = D / 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    inv = 1.0f / sqrtf(ss / (float)D + p.eps);
+                }
+                if (idx < G * (D / 8)) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (p.qw != nullptr) x[i] = x[i] * inv * fd_weight(p.qw, p.w_f32, 8 * ch + i);
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        const int pr = 4 * ch + h;
+                        if (p.cos_t != nullptr && pr < p.rot_pairs) {
+                            const float cs = p.cos_t[(size_t)tok * p.rot_pairs + pr], sn = p.sin_t[(size_t)tok * p.rot_pairs + pr];
+                            const float r0 = x[2 * h] * cs - x[2 * h + 1] * sn;
+                            const float r1 = x[2 * h] * sn + x[2 * h + 1] * cs;
+                            x[2 * h] = r0; x[2 * h + 1] = r1;
+                        }
+                    }
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&qv[c]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) h2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                }
+            }
+        };
         auto store_q = [&](int buf) {
 #pragma unroll
             for (int c = 0; c < QCHUNKS; ++c) {
@@ -823,7 +940,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         FdItem w, wn;
         int it = (int)blockIdx.x - (int)gridDim.x;
         bool have = fd_next(p, it, w);
-        if (have) { fetch_q(w); store_q(0); }
+        if (have) { fetch_q(w); finish_q(w); store_q(0); }
         while (have) {
             int it_next = it;
             const bool have_next = fd_next(p, it_next, wn);
@@ -881,7 +998,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 fa_fence_async_smem();
                 __syncwarp();
                 if (lane == 0) fa_mbar_arrive(p_ready);
-                if (j == 0 && have_next) store_q((ic + 1) & 1);     // the next item's queries, fetched above
+                if (j == 0 && have_next) { finish_q(wn); store_q((ic + 1) & 1); }     // the next item's queries, fetched above
             }
             // ---------------- the item's result ----------------
             alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (7u << 24) | t, failed);
@@ -1031,11 +1148,19 @@ PI_EXPORT int pi_attention_decode_tcgen05_supported(int page_size, int group) {
 // Segments of one token only (the others are skipped).  Requests whose keys are cut into more than one range
 // leave (max, sum, accumulator) per range in part_ml / part_acc for attn_merge_kernel; split_keys must be a
 // multiple of 128.
-PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
-                                          const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
-                                          const int* seg_start, const int* seg_len, void* out, float* part_acc, float* part_ml,
-                                          int max_splits, int split_keys, int num_segments, int nq, int nkv, int page_size,
-                                          int window, float scale, cudaStream_t stream) {
+// what the fused form needs beside the arguments of pi_attention_decode_tcgen05
+struct FdFusion {
+    int fuse;
+    const void* qw; const void* kw; int w_f32; float eps;
+    const float* cos_t; const float* sin_t; int rot_pairs;
+    int* error_count;
+};
+
+static int fd_launch(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
+                     const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                     const int* seg_start, const int* seg_len, void* out, float* part_acc, float* part_ml,
+                     int max_splits, int split_keys, int num_segments, int nq, int nkv, int page_size,
+                     int window, float scale, const FdFusion& fusion, cudaStream_t stream) {
     if (num_segments <= 0) return 0;
     if (!(scale > 0.0f)) return pi_refuse("pi_attention_decode_tcgen05: the score scale must be positive");
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return pi_refuse("pi_attention_decode_tcgen05: nq=%d must be a positive multiple of nkv=%d", nq, nkv);
@@ -1061,6 +1186,9 @@ PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const voi
     p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.page_size = page_size; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.num_segments = num_segments; p.split_keys = split_keys; p.num_items = (int)items;
+    p.fuse = fusion.fuse; p.kpool = (bf16*)kcache; p.vpool = (bf16*)vcache;
+    p.qw = fusion.qw; p.kw = fusion.kw; p.w_f32 = fusion.w_f32; p.eps = fusion.eps;
+    p.cos_t = fusion.cos_t; p.sin_t = fusion.sin_t; p.rot_pairs = fusion.rot_pairs; p.error_count = fusion.error_count;
     static int sms = 0;
     static bool configured = false;
     constexpr unsigned tile_bytes = (PI_HEAD_DIM / 64) * 128 * 128;
@@ -1083,6 +1211,41 @@ PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const voi
     else if (p.group <= 8) pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 8>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
     else pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 16>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
     return pi_check_launch("pi_attention_decode_tcgen05");
+}
+
+PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
+                                          const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                                          const int* seg_start, const int* seg_len, void* out, float* part_acc, float* part_ml,
+                                          int max_splits, int split_keys, int num_segments, int nq, int nkv, int page_size,
+                                          int window, float scale, cudaStream_t stream) {
+    const FdFusion none = {0, nullptr, nullptr, 0, 0.0f, nullptr, nullptr, 0, nullptr};
+    return fd_launch(q, q_stride, kcache, vcache, num_pages, block_table, bt_stride, seg_off, seg_slot, seg_start, seg_len, out,
+                     part_acc, part_ml, max_splits, split_keys, num_segments, nq, nkv, page_size, window, scale, none, stream);
+}
+
+// The same for a step of single tokens straight from the q/k/v product: `qkv` [T, q_stride] holds nq query heads,
+// nkv key heads and nkv value heads per token, all raw.  Per-head RMSNorm of queries and keys (weights q_weight /
+// k_weight [D] in bf16 or float32 (weight_dtype), eps; both null: no norm), rotation of adjacent pairs (2i, 2i + 1)
+// by cos_t / sin_t [T, rot_pairs] (null: none) and the write of every token's key and value into its page happen
+// inside the attention kernel; no other kernel has to touch qkv or the pages for these tokens.  A token whose page
+// is missing is counted in *error_count and not written.  Every segment must be a single token.
+PI_EXPORT int pi_attention_decode_tcgen05_fused(const void* qkv, int q_stride, void* kcache, void* vcache, long long num_pages,
+                                                const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
+                                                const int* seg_start, const int* seg_len, void* out, float* part_acc,
+                                                float* part_ml, int max_splits, int split_keys, int num_segments, int nq,
+                                                int nkv, int page_size, int window, float scale, const void* q_weight,
+                                                const void* k_weight, int weight_dtype, float eps, const float* cos_t,
+                                                const float* sin_t, int rot_pairs, int* error_count, cudaStream_t stream) {
+    if ((q_weight == nullptr) != (k_weight == nullptr)) return pi_refuse("pi_attention_decode_tcgen05_fused: give both norm weights or none");
+    if (q_weight != nullptr && weight_dtype != PI_F32 && weight_dtype != PI_BF16)
+        return pi_refuse("pi_attention_decode_tcgen05_fused: unknown dtype code %d of the norm weights", weight_dtype);
+    if ((cos_t == nullptr) != (sin_t == nullptr) || rot_pairs < 0 || rot_pairs * 2 > PI_HEAD_DIM)
+        return pi_refuse("pi_attention_decode_tcgen05_fused: rotation tables / rot_pairs=%d do not fit head size %d", rot_pairs, PI_HEAD_DIM);
+    if (error_count == nullptr) return pi_refuse("pi_attention_decode_tcgen05_fused: error_count is needed");
+    if (q_stride < (nq + 2 * nkv) * PI_HEAD_DIM) return pi_refuse("pi_attention_decode_tcgen05_fused: rows of %d elements cannot hold %d + 2 x %d heads", q_stride, nq, nkv);
+    const FdFusion fusion = {1, q_weight, k_weight, weight_dtype == PI_F32 ? 1 : 0, eps, cos_t, sin_t, rot_pairs, error_count};
+    return fd_launch(qkv, q_stride, kcache, vcache, num_pages, block_table, bt_stride, seg_off, seg_slot, seg_start, seg_len, out,
+                     part_acc, part_ml, max_splits, split_keys, num_segments, nq, nkv, page_size, window, scale, fusion, stream);
 }
 
 #else   // head sizes this kernel does not take

@@ -433,6 +433,67 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
     return out
 
 
+FUSE_ROPE = os.environ.get("PULSE_FUSE_ROPE", "1") != "0"     # steps of single tokens: norm, rotation and page write inside the attention kernel
+
+
+def attention_decode_fused_usable(head_dim: int, page_size: int, group: int, split_keys: int, adjacent_pairs: bool,
+                                  act_dtype: torch.dtype) -> bool:
+    """Whether a step that holds single tokens only can leave per-head norm, rotation and the page write of the new
+    keys and values to the tcgen05 decode attention kernel (``attention_decode_fused``)."""
+    return (FUSE_ROPE and TCGEN05_DECODE and act_dtype == torch.bfloat16 and adjacent_pairs and split_keys % 128 == 0
+            and attention_decode_tcgen05_usable(head_dim, page_size, group))
+
+
+def attention_decode_fused(qkv: torch.Tensor, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg,
+                           num_segments: int, max_splits: int, part_acc, part_ml, nq: int, nkv: int, head_dim: int,
+                           page_size: int, window: int | None, scale: float, q_weight, k_weight, eps: float, cos, sin,
+                           error_count: torch.Tensor, split_keys: int = SPLIT_KEYS, out: torch.Tensor | None = None,
+                           prefetch: torch.Tensor | None = None) -> torch.Tensor:
+    """A step of single tokens, straight from the q/k/v product: ``qkv`` [T, (nq + 2 nkv) d] raw.  The tcgen05 decode
+    kernel normalises and rotates the queries as it loads them, and writes each token's (normalised, rotated) key
+    and its value into their page before it reads that page; the ranges of a split request are then merged as in
+    ``attention_mma``.  ``q_weight``/``k_weight`` None: no per-head norm; ``cos``/``sin`` None: no rotation (pairs are
+    adjacent elements).  Returns [T, nq * d]."""
+    _need_cuda(qkv, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml,
+               q_weight, k_weight, cos, sin, error_count)
+    _need_contig(qkv=qkv, kcache=kcache, vcache=vcache, block_table=block_table, cos=cos, sin=sin)
+    T, width = qkv.shape
+    if qkv.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or vcache.dtype != torch.bfloat16:
+        raise KernelError("the fused decode attention takes bfloat16 only")
+    if width != (nq + 2 * nkv) * head_dim or T != num_segments:
+        raise KernelError("the fused decode attention takes one row of (nq + 2 nkv) * d raw projections per single-token segment")
+    if kcache.shape[1:] != (nkv, page_size, head_dim) or vcache.shape != kcache.shape:
+        raise KernelError(f"pages must be [n, {nkv}, {page_size}, {head_dim}], got {tuple(kcache.shape)}")
+    has_norm = q_weight is not None
+    if has_norm and (k_weight is None or q_weight.shape != (head_dim,) or k_weight.shape != (head_dim,)
+                     or q_weight.dtype != k_weight.dtype):
+        raise KernelError("per-head norm weights must both have shape (head_dim,) and one dtype")
+    rot_pairs = 0 if cos is None else cos.shape[1]
+    if cos is not None and (cos.shape != (T, rot_pairs) or sin.shape != cos.shape or cos.dtype != torch.float32):
+        raise KernelError("rotation tables must be float32 [T, pairs]")
+    if max_splits > 1:
+        need = T * nq * max_splits
+        if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:
+            raise KernelError("scratch for the split decode attention is missing or too small")
+    if out is None:
+        out = torch.empty((T, nq * head_dim), dtype=qkv.dtype, device=qkv.device)
+    tlib = _lib("attention_tcgen05", head_dim)
+    _check(tlib, tlib.pi_attention_decode_tcgen05_fused(
+        _p(qkv), c_int(width), _p(kcache), _p(vcache), ctypes.c_longlong(kcache.shape[0]), _p(block_table),
+        c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), _p(part_acc), _p(part_ml),
+        c_int(max_splits), c_int(split_keys), c_int(num_segments), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0),
+        c_float(scale), _p(q_weight), _p(k_weight), c_int(_code(q_weight.dtype) if has_norm else BF16), c_float(eps), _p(cos),
+        _p(sin), c_int(rot_pairs), _p(error_count), _stream()), "attention_decode_tcgen05_fused")
+    if max_splits > 1:      # the merge of the key ranges stays with the mma library
+        lib = _lib("attention_mma", head_dim)
+        _check(lib, lib.pi_attention_mma_prefetch(
+            _p(qkv), c_int(width), _p(kcache), _p(vcache), _p(block_table), c_int(block_table.shape[1]), _p(seg_off),
+            _p(seg_slot), _p(seg_start), _p(seg_len), _p(token_seg), _p(out), _p(part_acc), _p(part_ml), c_int(max_splits),
+            c_int(split_keys), c_int(T), c_int(num_segments), c_int(1), c_int(0), c_int(2), c_int(nq), c_int(nkv),
+            c_int(page_size), c_int(window or 0), c_float(scale), *_prefetch_args(prefetch), _stream()), "attention merge")
+    return out
+
+
 # ---- matrix products -----------------------------------------------------------------------------------------------
 def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """x fp32 [M, K], weight fp32 [N, K] -> fp32 [M, N] with fp32 FMA in a fixed k order."""

@@ -94,14 +94,26 @@ class Attention(Mixer):
         nkv_written = self.num_kv_heads if self.writes_cache else 0
         qkv = ops.linear(x, self.qkv, ctx.act_dtype)
         rot = ctx.position_data.get(self.position) if self.position else None
+        use_mma = (ctx.act_dtype == torch.bfloat16 and self.attention_impl != "simple"
+                   and self.head_dim % 16 == 0 and self.head_dim <= 256)
+        if use_mma and self.writes_cache and ctx.has_decode and not ctx.has_prompt and qkv.is_contiguous():
+            # a step of single tokens: per-head norm, rotation and the page write happen inside the attention kernel
+            scratch = ctx.attention_scratch(self.num_heads, self.head_dim, self.window, self.num_kv_heads)
+            if ops.attention_decode_fused_usable(self.head_dim, cache.page_size, self.num_heads // self.num_kv_heads,
+                                                 scratch.split_keys, rot["adjacent"] if rot else True, ctx.act_dtype):
+                attn = ops.attention_decode_fused(
+                    qkv, cache.keys, cache.values, cache.block_table, ctx.seg_off, ctx.seg_slot, ctx.seg_start, ctx.seg_len,
+                    ctx.token_seg, ctx.num_segments, scratch.max_splits, scratch.acc, scratch.ml, self.num_heads,
+                    self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale, self.q_norm, self.k_norm,
+                    self.norm_eps, rot["cos"] if rot else None, rot["sin"] if rot else None, ctx.error_count,
+                    split_keys=scratch.split_keys, prefetch=ctx.prefetch(getattr(ctx, "upcoming_weights", None)))
+                return ops.linear(attn, self.o, ctx.act_dtype, residual=residual, next_norm=next_norm)
         ops.qk_norm_rope_write(
             qkv, self.q_norm, self.k_norm, self.norm_eps,
             rot["cos"] if rot else None, rot["sin"] if rot else None, rot["adjacent"] if rot else True,
             cache.keys, cache.values, cache.block_table, ctx.token_slot, ctx.positions, cache.page_size,
             self.num_heads, nkv_written, self.head_dim, ctx.error_count, prefetch=ctx.prefetch(self.o))
         q_stride = qkv.shape[1]
-        use_mma = (ctx.act_dtype == torch.bfloat16 and self.attention_impl != "simple"
-                   and self.head_dim % 16 == 0 and self.head_dim <= 256)
         if use_mma:
             scratch = ctx.attention_scratch(self.num_heads, self.head_dim, self.window, self.num_kv_heads)
             attn = ops.attention_mma(

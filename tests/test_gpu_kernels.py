@@ -269,6 +269,71 @@ def test_attention_tcgen05_long_portions(nq, nkv, d, page, window):
     assert err < 0.03
 
 
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 8), (16, 1, 64, 64), (32, 8, 128, 16), (5, 5, 128, 32), (12, 2, 64, 16)])
+@pytest.mark.parametrize("window", [None, 300])
+@pytest.mark.parametrize("norm,rot", [(True, 1.0), (True, 0.5), (False, 1.0), (True, 0.0)])
+def test_attention_decode_fused_matches_the_separate_kernels(nq, nkv, d, page, window, norm, rot):
+    """A step of single tokens with per-head norm, rotation and the page write done inside the tcgen05 decode kernel,
+    against the separate kernels (qk_norm_rope_write, then attention): the same keys and values in the pages (values
+    bitwise, keys to one rounding), untouched pages untouched, the same attention output; requests of 1 to 1,300
+    keys, so that the newest key sits in a first, a middle and a last tile and ranges are split."""
+    dev, ops = need_gpu(), _ops()
+    lengths = [1, 17, 128, 129, 700, 1300, 513, 64]
+    segs = [(i, n - 1, 1) for i, n in enumerate(lengths)]
+    kv = PagedKV(lengths, nkv, d, page, torch.bfloat16, dev, seed=nq + d, fill_garbage=False)
+    meta = segments_to_device(segs, dev)
+    T = meta["T"]
+    g = torch.Generator().manual_seed(d + page)
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, generator=g).to(torch.bfloat16).to(dev)
+    qw = (1 + 0.3 * torch.randn(d, generator=g)).to(torch.bfloat16).to(dev) if norm else None
+    kw = (1 + 0.3 * torch.randn(d, generator=g)).to(torch.bfloat16).to(dev) if norm else None
+    pairs = int(d // 2 * rot)
+    cos = sin = None
+    if pairs:
+        ang = torch.rand(T, pairs, generator=g) * 6.28
+        cos, sin = torch.cos(ang).to(dev), torch.sin(ang).to(dev)
+    eps, scale = 1e-5, 1.0 / math.sqrt(d)
+    split_keys = 256
+    splits = max(ops.attention_num_splits(st, window, split_keys) for _, st, _ in segs)
+    err1 = torch.zeros(1, dtype=torch.int32, device=dev)
+    err2 = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def scratch():
+        return (torch.empty(T * nq * splits * d, dtype=torch.float32, device=dev),
+                torch.empty(T * nq * splits * 2, dtype=torch.float32, device=dev))
+    # the separate kernels
+    k1, v1, q1 = kv.kcache.clone(), kv.vcache.clone(), qkv.clone()
+    ops.qk_norm_rope_write(q1, qw, kw, eps, cos, sin, True, k1, v1, kv.table_dev, meta["token_slot"], meta["positions"], page,
+                           nq, nkv, d, err1)
+    acc, ml = scratch()
+    want = ops.attention_mma(q1, q1.shape[1], k1, v1, kv.table_dev, meta["seg_off"], meta["seg_slot"], meta["seg_start"],
+                             meta["seg_len"], meta["token_seg"], T, T, 1, False, True, splits, acc, ml, nq, nkv, d, page, window,
+                             scale, split_keys=split_keys)
+    # one kernel
+    k2, v2 = kv.kcache.clone(), kv.vcache.clone()
+    acc, ml = scratch()
+    got = ops.attention_decode_fused(qkv.clone(), k2, v2, kv.table_dev, meta["seg_off"], meta["seg_slot"], meta["seg_start"],
+                                     meta["seg_len"], meta["token_seg"], T, splits, acc, ml, nq, nkv, d, page, window, scale,
+                                     qw, kw, eps, cos, sin, err2, split_keys=split_keys)
+    assert ops.attention_tcgen05_status(d) == 0 and int(err1.item()) == 0 and int(err2.item()) == 0
+    assert torch.equal(v2, v1)                                           # values: a copy
+    kd = (k2.float() - k1.float()).abs()
+    assert float(kd.max()) <= 2 ** -7 * float(k1.float().abs().max())    # keys: the same arithmetic, at most a rounding apart
+    changed = (k2 != kv.kcache).flatten(2).any(-1).sum().item()          # (page, head) rows that were written
+    assert 0 < changed <= T * nkv
+    diff = float((got.float() - want.float()).abs().max())
+    assert diff <= 2e-2 * float(want.float().abs().max()) + 1e-3, diff
+    # a missing page is counted, not written
+    bad = kv.table_dev.clone()
+    bad[5, (lengths[5] - 1) // page] = -1
+    k3, v3 = kv.kcache.clone(), kv.vcache.clone()
+    acc, ml = scratch()
+    ops.attention_decode_fused(qkv.clone(), k3, v3, bad, meta["seg_off"], meta["seg_slot"], meta["seg_start"], meta["seg_len"],
+                               meta["token_seg"], T, splits, acc, ml, nq, nkv, d, page, window, scale, qw, kw, eps, cos, sin, err2,
+                               split_keys=split_keys)
+    assert int(err2.item()) == nkv and ops.attention_tcgen05_status(d) == 0
+
+
 @pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 8), (4, 1, 64, 128), (32, 8, 128, 16)])
 @pytest.mark.parametrize("window", [None, 130, 900])
 @pytest.mark.parametrize("shares", [2, 3, 7, 16])
