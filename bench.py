@@ -108,9 +108,10 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_config(layers: int):
+def make_config(layers: int, shape: dict | None = None):
     from pulse_infer_b200.config import Qwen3Config
-    return Qwen3Config(architecture="Qwen3ForCausalLM", torch_dtype="bfloat16", eos_token_ids=(), **{**SHAPE, "num_hidden_layers": layers})
+    return Qwen3Config(architecture="Qwen3ForCausalLM", torch_dtype="bfloat16", eos_token_ids=(),
+                       **{**(shape or SHAPE), "num_hidden_layers": layers})
 
 
 def weight_bytes_per_step(cfg) -> int:
@@ -249,7 +250,8 @@ def run_part(args) -> dict:
     import numpy as np
     global PROFILER_RANGE
     PROFILER_RANGE = True
-    cfg = make_config(args.layers or FULL_LAYERS)
+    shape = WORKLOADS[args.shape]["shape"] if args.shape else SHAPE
+    cfg = make_config(args.layers or shape["num_hidden_layers"], shape)
     rng = np.random.RandomState(0)
     if args.only == "prefill":
         T = args.prompt_len or PROMPT
@@ -257,13 +259,13 @@ def run_part(args) -> dict:
         ms = timed_prefill(engine, rng, repeats=max(1, args.steps), prompt=T, cached=args.cached)
         peaks, _ = load_peaks()
         flops = prefill_flops(cfg, T) + 4.0 * cfg.num_attention_heads * cfg.head_dim * T * args.cached * cfg.num_hidden_layers
-        return {"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": T, "cached": args.cached, "ms": round(ms, 3),
+        return {"only": "prefill", "shape": args.shape or "bench", "layers": cfg.num_hidden_layers, "tokens": T, "cached": args.cached, "ms": round(ms, 3),
                 "tokens_per_s": round(T / ms * 1e3, 1), "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
     prompt = args.prompt_len or min(PROMPT, args.context - args.steps - args.warmup - 1)
     engine = make_engine(cfg, args.batch, graphs=not args.no_graphs, context=args.context, prompt=prompt)
     ms, launches, ctx, _, _ = timed_decode(engine, args.batch, args.steps, args.warmup, rng, False, context=args.context,
                                            prompt=prompt)
-    return {"only": "decode", "layers": cfg.num_hidden_layers, "batch": args.batch, "context": args.context,
+    return {"only": "decode", "shape": args.shape or "bench", "layers": cfg.num_hidden_layers, "batch": args.batch, "context": args.context,
             "ms_per_step": round(ms, 4), "tokens_per_s": round(args.batch / ms * 1e3, 1), "gpu_launches": launches,
             "cuda_graphs": not args.no_graphs}
 
@@ -375,21 +377,31 @@ def run_workload(args) -> dict:
     wid = engine.add_request(prompts[0][:64], 4, ignore_eos=True)
     engine.run_until_complete()
     assert len(engine.get_result(wid)) == 4
+    t_warm = time.time()
+    recorded_before = 0 if args.no_warm_up else engine.warm_up()      # decode steps of every batch size, as a server does at start
     torch.cuda.synchronize()
+    warm_s = time.time() - t_warm
 
     ids = [engine.add_request(p, w["new_tokens"], ignore_eos=True) for p in prompts]
+    graphs = engine.runner.graphs
+    rec0, rec_s0 = (graphs.recordings, graphs.record_seconds) if graphs is not None else (0, 0.0)
     kinds, host_ms, events = [], [], []
     clocks = ClockSampler()
     clocks.start()
     time.sleep(0.3)
     c0 = time.monotonic()
     t0 = time.perf_counter()
+    first, last = ([int(v) for v in args.profile_steps.split(":")] if args.profile_steps else (-1, -1))
     while engine.has_work():
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if len(kinds) == first:
+            torch.cuda.profiler.start()
         h0 = time.perf_counter()
         a.record()
         engine.step()
         b.record()
+        if len(kinds) == last:
+            torch.cuda.profiler.stop()
         host_ms.append((time.perf_counter() - h0) * 1e3)
         batch = engine.engine.last_batch
         sizes = [n for _, n in batch.entries]
@@ -406,7 +418,8 @@ def run_workload(args) -> dict:
         idx = [i for i, k in enumerate(kinds) if k == kind]
         if idx:
             per_kind[kind] = {"steps": len(idx), "host_ms": round(sum(host_ms[i] for i in idx) / len(idx), 3),
-                              "gpu_ms": round(sum(gpu_ms[i] for i in idx) / len(idx), 3)}
+                              "gpu_ms": round(sum(gpu_ms[i] for i in idx) / len(idx), 3),
+                              "gpu_ms_median": round(statistics.median(gpu_ms[i] for i in idx), 3)}
     st = engine.get_stats()
     prompt_tokens = sum(lengths)
     return {"workload": args.workload, "impl": "ours", "dtype": "bf16", "layers": cfg.num_hidden_layers,
@@ -416,6 +429,9 @@ def run_workload(args) -> dict:
             "seconds": round(wall_s, 3), "generated_tokens_per_s": round(generated / wall_s, 1),
             "all_tokens_per_s": round((generated + prompt_tokens) / wall_s, 1), "steps": len(kinds), "step_kinds": per_kind,
             "gpu_busy_frac": round(sum(gpu_ms) / (wall_s * 1e3), 3), "preemptions": st.num_preemptions,
+            "graphs_recorded_at_start": recorded_before, "warm_up_s": round(warm_s, 2),
+            "graphs_recorded": graphs.recordings - rec0 if graphs is not None else 0,
+            "graph_record_s": round(graphs.record_seconds - rec_s0, 3) if graphs is not None else 0.0,
             "weight_gb": round(engine.runner.model.weight_bytes() / 1e9, 2), "clocks": clock_info, "build_s": round(build_s, 1),
             "data": "synthetic: seeded uniform-random token ids, seeded random weights"}
 
@@ -500,10 +516,17 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=None, help="with --only: tokens of each prompt (default 2048)")
     ap.add_argument("--cached", type=int, default=0, help="with --only prefill: tokens of the request already in the cache")
     ap.add_argument("--no-graphs", action="store_true", help="with --only: launch decode steps eagerly")
+    ap.add_argument("--shape", choices=sorted(WORKLOADS), default=None,
+                    help="with --only: the layer sizes of that workload's model instead of the Qwen3-8B shape")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                     help="a whole serving run through Engine and the scheduler instead of the decode benchmark")
-    ap.add_argument("--chunk", type=int, default=512, help="with --workload: longest prompt portion of one request")
+    ap.add_argument("--profile-steps", default=None, metavar="A:B",
+                    help="with --workload: cudaProfilerStart before step A, cudaProfilerStop after step B "
+                         "(ncu --profile-from-start off)")
+    ap.add_argument("--no-warm-up", action="store_true",
+                    help="with --workload: do not record the decode steps of all batch sizes before the timed run")
+    ap.add_argument("--chunk", type=int, default=1024, help="with --workload: longest prompt portion of one request")
     ap.add_argument("--budget", type=int, default=2048, help="with --workload: tokens of one step")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -548,33 +548,48 @@ __global__ void attn_prompt_merge_kernel(const float* __restrict__ part_acc, con
 
 // =============================================================================================================
 // Decode: segments of one token.  The work is all memory traffic - every key and value of the request is read
-// once for a handful of query rows - so the kernel is built around keeping HBM busy: a persistent CTA per SM
-// walks a list of (request, kv head, key range) items, and its TMA producer warp runs ahead through a ring of
-// key/value tiles ACROSS item boundaries, so the ring never drains while an item finishes.
+// once for a handful of query rows - so the kernel is built around keeping HBM busy: one persistent CTA per SM,
+// whose TMA producer warp runs ahead through a ring of key/value tiles ACROSS the boundaries of its pieces of
+// work, so the ring never drains while a piece finishes.
 //   S^T = K Q^T     tcgen05.mma M 128 (keys of the tile) x N 16 (the group's query heads, padded): the key tile
 //                   that TMA delivered is the A operand as it lies; the scores land in tensor memory with one
 //                   key per lane
 //   softmax         four warps, thread = key: column maxima by warp shuffles and one exchange through shared
 //                   memory per tile; every thread keeps the running maxima (the same in all threads) and the
-//                   sum over ITS keys, which is reduced across threads once per item
+//                   sum over ITS keys, which is reduced across threads once per piece
 //   O^T += V^T P^T  tcgen05.mma M 128 (head dimension) x N 16, A = the value tile MN-major, B = the
 //                   probabilities [16 heads, 128 keys] from shared memory
-// An item with the only key range of its request writes the output; otherwise it writes (max, sum, accumulator)
-// in the layout attn_merge_kernel of attention_mma.cu combines.  Key ranges are those of the mma.sync decode
-// kernel: they depend on the request's own length only.
-// Needs a group of at most 16 query heads per kv head and pages of at most 64 keys.
+// Work split.  The key tiles (128 keys) of all (request, kv head) pairs of the step form one sequence - request after
+// request, kv head after kv head, oldest tile first, each pair preceded by `pair_cost` units that stand for the fixed
+// cost of starting and finishing it - and every CTA takes an equal span of it, whatever the lengths of the requests
+// are: a span may end in the middle of a pair and the next CTA goes on from there.  A pair that lies inside one span
+// is finished by its CTA.  A pair that was cut leaves (max, sum, accumulator) per piece in a scratch that is indexed
+// by CTA (a span has at most one piece that began before it and one that goes on behind it, so two slots per CTA do
+// for any batch and any context); when a CTA has done its span it reports its pieces, and the CTA that reports the
+// pair's last missing piece - a counter per pair tells - adds the pieces up in the order of the keys and writes the
+// output.  Nothing waits for another CTA.  The cuts depend on the whole step, so a request's result depends on its
+// neighbours by rounding.
+// Warps: 0 TMA producer, 1 MMA issuer, 2-5 softmax and output, 6 (fused mode) the writer of the new tokens' keys and
+// values, which runs ahead of the producer.
+// Needs a group of at most 16 query heads per kv head, pages of at most 64 keys, at most FD_MAX_SEGS segments.
 // =============================================================================================================
-#define FD_THREADS 192
+#define FD_THREADS 224
 #define FD_STAGES (PI_HEAD_DIM == 128 ? 3 : 6)
+#define FD_MAX_SEGS 1024
 
 struct FdParams {
     const bf16* q; int q_stride;
     const int* block_table; int bt_stride;
     const int* seg_off; const int* seg_slot; const int* seg_start; const int* seg_len;
-    bf16* out; float* part_acc; float* part_ml; int max_splits;
+    bf16* out;
+    float* ws_acc;            // [CTAs][2 slots][16 heads][D]   accumulators of pieces of cut pairs
+    float* ws_ml;             // [CTAs][2 slots][16 heads][2]   their (max, sum)
+    unsigned* ws_count;       // [CTAs] pieces delivered of the pair that BEGINS in that CTA's span; zero between launches
+    int span_min;             // shortest span in units
+    int pair_cost;            // units a pair counts for beside its tiles
     // fuse = 1: q holds the raw q/k/v projections of the step's tokens [T, (nq + 2 nkv) D].  The kernel then does what
-    // qk_norm_rope_write_kernel (elementwise.cu) does for single tokens: the queries of an item are normalised per head
-    // and rotated as they are loaded; the item that holds a request's newest position normalises and rotates that
+    // qk_norm_rope_write_kernel (elementwise.cu) does for single tokens: the queries of a piece are normalised per head
+    // and rotated as they are loaded; the piece that holds a request's newest position normalises and rotates that
     // token's key, writes it and the value into their page, and only then requests the tile that contains it.
     int fuse;
     bf16* kpool; bf16* vpool;            // [pages][nkv][page_size][D]
@@ -585,31 +600,82 @@ struct FdParams {
     int nq, nkv, group;
     int page_size, window;
     float scale_log2;
-    int num_segments, split_keys, num_items;
+    int num_segments;
 };
 
+// a piece: tiles [j0, j0 + ntiles) of the pair (seg, kvh)
 struct FdItem {
-    int seg, kvh, split, nsplits, pos, lo, kb, ke, ntiles;
+    int seg, kvh, pos, lo, kb, ke, ntiles;
+    int whole;        // the piece is the whole pair: its CTA writes the output
+    int newest;       // the piece holds the pair's last tile (with the newest key)
+    int slot;         // scratch slot of a piece of a cut pair: 1 if the pair begins in this span, else 0
+    int cta_first;    // CTA whose span holds the pair's first tile
+    int pieces;       // spans the pair reaches into
 };
 
-// item `it` of the box [max_splits][segments][kv heads] (key ranges slowest, so that the items that exist come first)
-__device__ __forceinline__ bool fd_item(const FdParams& p, int it, FdItem& w) {
-    w.kvh = it % p.nkv;
-    const int rest = it / p.nkv;
-    w.seg = rest % p.num_segments;
-    w.split = rest / p.num_segments;
-    if (p.seg_len[w.seg] != 1) return false;
-    w.pos = p.seg_start[w.seg];
-    w.lo = fa_window_lo(w.pos, p.window);
-    const int lo_al = (w.lo / 64) * 64;
-    // never more ranges than the scratch has room for: with a bound smaller than the request needs, the last range
-    // runs on to the newest key (the same rule as decode_ranges in attention_mma.cu, whose merge kernel follows)
-    w.nsplits = min((w.pos + 1 - lo_al + p.split_keys - 1) / p.split_keys, p.max_splits);
-    if (w.split >= w.nsplits) return false;
-    w.kb = lo_al + w.split * p.split_keys;
-    w.ke = w.split + 1 < w.nsplits ? min(w.kb + p.split_keys, w.pos + 1) : w.pos + 1;
-    w.ntiles = (w.ke - w.kb + FA_BN - 1) / FA_BN;
-    return true;
+// key tiles of a segment's pairs: from the window's first key (rounded down to 64) to the newest one; 0 if the
+// segment is not a single token
+__device__ __forceinline__ int fd_seg_tiles(const FdParams& p, int seg) {
+    if (p.seg_len[seg] != 1) return 0;
+    const int pos = p.seg_start[seg];
+    const int lo_al = (fa_window_lo(pos, p.window) / 64) * 64;
+    return (pos + 1 - lo_al + FA_BN - 1) / FA_BN;
+}
+
+struct FdCursor { int f, end, seg, span; };
+
+// tile_pre[s] = tiles per kv head of the segments before s, dec_pre[s] = single-token segments before s (shared
+// memory); the sequence's first unit of segment s
+__device__ __forceinline__ int fd_seg_unit(const FdParams& p, const int* tile_pre, int s) {
+    return p.nkv * (tile_pre[s] + p.pair_cost * tile_pre[FD_MAX_SEGS + 1 + s]);
+}
+
+// the CTA's span
+__device__ __forceinline__ void fd_begin(const FdParams& p, const int* tile_pre, FdCursor& c) {
+    const int total = fd_seg_unit(p, tile_pre, p.num_segments);
+    c.span = max((total + (int)gridDim.x - 1) / (int)gridDim.x, p.span_min);
+    const long long b = (long long)blockIdx.x * c.span;
+    c.f = (int)(b < total ? b : total);
+    c.end = min(c.f + c.span, total);
+    // the last segment whose first unit is not behind f
+    int lo = 0, hi = p.num_segments;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (fd_seg_unit(p, tile_pre, mid) <= c.f) lo = mid; else hi = mid;
+    }
+    c.seg = lo;
+}
+
+// the next piece of this CTA's span
+__device__ __forceinline__ bool fd_next(const FdParams& p, const int* tile_pre, FdCursor& c, FdItem& w) {
+    while (c.f < c.end) {
+        while (fd_seg_unit(p, tile_pre, c.seg + 1) <= c.f) ++c.seg;      // ends: f is before the end of the sequence
+        const int n = tile_pre[c.seg + 1] - tile_pre[c.seg];
+        const int per = n + p.pair_cost;
+        const int rel = c.f - fd_seg_unit(p, tile_pre, c.seg);
+        const int tile0 = c.f - rel % per + p.pair_cost;                  // unit of the pair's first tile
+        const int lo_u = max(c.f, tile0), hi_u = min(c.end, tile0 + n);
+        if (hi_u <= lo_u) {          // the span ends among the pair's cost units: its tiles are the next CTA's
+            c.f = c.end;
+            break;
+        }
+        const int j0 = lo_u - tile0;
+        w.seg = c.seg;
+        w.kvh = rel / per;
+        w.ntiles = hi_u - lo_u;
+        w.pos = p.seg_start[w.seg];
+        w.lo = fa_window_lo(w.pos, p.window);
+        w.kb = (w.lo / 64) * 64 + j0 * FA_BN;
+        w.newest = (j0 + w.ntiles == n) ? 1 : 0;
+        w.ke = w.newest ? w.pos + 1 : w.kb + w.ntiles * FA_BN;
+        w.whole = (j0 == 0 && w.newest) ? 1 : 0;
+        w.slot = j0 == 0 ? 1 : 0;
+        w.cta_first = tile0 / c.span;
+        w.pieces = (tile0 + n - 1) / c.span - w.cta_first + 1;
+        c.f = hi_u;
+        return true;
+    }
+    return false;
 }
 
 // GP (4, 8 or 16) columns of a row of tensor memory
@@ -659,10 +725,19 @@ __device__ __forceinline__ void fd_softmax_sync() {       // the four softmax wa
     asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-// the next item of this CTA that exists, starting behind `it`
-__device__ __forceinline__ bool fd_next(const FdParams& p, int& it, FdItem& w) {
-    for (it += gridDim.x; it < p.num_items; it += gridDim.x)
-        if (fd_item(p, it, w)) return true;
+// a counter in shared memory that another warp of the CTA raises: bounded like the waits on barriers
+__device__ __forceinline__ void fd_set_count(int* counter, int value) {
+    asm volatile("st.release.cta.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(counter)), "r"(value) : "memory");
+}
+__device__ __forceinline__ bool fd_wait_count(int* counter, int want, unsigned code, volatile unsigned* failed) {
+    for (unsigned spin = 0; spin < FA_SPIN_LIMIT; ++spin) {
+        int have;
+        asm volatile("ld.acquire.cta.shared::cta.b32 %0, [%1];" : "=r"(have) : "r"(fa_smem(counter)) : "memory");
+        if (have >= want) return true;
+        if ((spin & 1023u) == 1023u && *failed) return false;
+    }
+    *failed = 1;
+    atomicCAS(&g_fa_status, 0u, code);
     return false;
 }
 
@@ -722,6 +797,61 @@ __device__ __forceinline__ void fd_write_new_token(const FdParams& p, const FdIt
     }
 }
 
+// The pieces of a cut pair, added up in the order of their keys by the 128 softmax threads (thread = element of the
+// head).  Piece i lies in the scratch of CTA cta_first + i: slot 1 there for the first one, slot 0 for the others.
+// The loads of a chunk of pieces are issued together for all heads of the group: a chain of L2 latencies otherwise.
+template <int D, int GP>
+__device__ __forceinline__ void fd_merge(const FdParams& p, const FdItem& w, int tok, int tid, int G) {
+    constexpr int PC = 32 / GP;          // pieces per chunk
+    const int e = tid < D ? tid : 0;
+    float mstar[GP], num[GP], den[GP];
+#pragma unroll
+    for (int g = 0; g < GP; ++g) { mstar[g] = -INFINITY; num[g] = 0.0f; den[g] = 0.0f; }
+    for (int i0 = 0; i0 < w.pieces; i0 += PC) {
+        float m[PC][GP];
+#pragma unroll
+        for (int i = 0; i < PC; ++i) {
+            const size_t r = ((size_t)(w.cta_first + i0 + i) * 2 + (i0 + i == 0 ? 1 : 0)) * 16;
+#pragma unroll
+            for (int g = 0; g < GP; ++g) m[i][g] = (i0 + i < w.pieces && g < G) ? __ldcg(p.ws_ml + (r + g) * 2) : -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < PC; ++i)
+#pragma unroll
+            for (int g = 0; g < GP; ++g) mstar[g] = fmaxf(mstar[g], m[i][g]);
+    }
+    for (int i0 = 0; i0 < w.pieces; i0 += PC) {
+        float2 ml[PC][GP];
+        float a[PC][GP];
+#pragma unroll
+        for (int i = 0; i < PC; ++i) {
+            const size_t r = ((size_t)(w.cta_first + i0 + i) * 2 + (i0 + i == 0 ? 1 : 0)) * 16;
+#pragma unroll
+            for (int g = 0; g < GP; ++g) {
+                const bool live = i0 + i < w.pieces && g < G;
+                ml[i][g] = live ? __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (r + g) * 2)) : make_float2(-INFINITY, 0.0f);
+                a[i][g] = live ? __ldcg(p.ws_acc + (r + g) * D + e) : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PC; ++i)
+#pragma unroll
+            for (int g = 0; g < GP; ++g) {
+                const float f = mstar[g] == -INFINITY ? 0.0f : fa_ex2(ml[i][g].x - mstar[g]);      // -inf gives 0
+                num[g] += f * a[i][g];
+                den[g] += f * ml[i][g].y;
+            }
+    }
+    if (tid < D) {
+#pragma unroll
+        for (int g = 0; g < GP; ++g)
+            if (g < G) {
+                const size_t row = (size_t)tok * p.nq + (size_t)w.kvh * G + g;
+                p.out[row * D + tid] = __float2bfloat16_rn(den[g] > 0.0f ? num[g] / den[g] : 0.0f);
+            }
+    }
+}
+
 // GP: the group's query heads rounded up to 4, 8 or 16
 template <int D, int GP>
 __global__ void __launch_bounds__(FD_THREADS, 1)
@@ -754,6 +884,9 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     unsigned long long* q_ready = s_full + 4;             // [2] softmax (4 warps) -> MMA: an item's queries are in place
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(s_full + 6);
     volatile unsigned* failed = tmem_slot + 1;
+    volatile int* merge_here = reinterpret_cast<volatile int*>(tmem_slot + 2);     // [2] softmax warps: this CTA adds the pieces of that pair up
+    int* tokens_written = reinterpret_cast<int*>(tmem_slot + 4);                   // writer warp -> producer: pairs whose new token is in its page
+    int* tile_pre = reinterpret_cast<int*>(tmem_slot + 6);                         // [FD_MAX_SEGS + 1] tiles, then [FD_MAX_SEGS + 1] segments
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.group;
@@ -763,7 +896,28 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         fa_mbar_init(p_ready, 4); fa_mbar_init(pv_done, 1);
         fa_mbar_init(&q_ready[0], 4); fa_mbar_init(&q_ready[1], 4);
         *failed = 0;
+        *tokens_written = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        // tiles per kv head, and single-token segments, before each segment: chunks of 32 segments, a warp scan in each.
+        // The step's metadata was written before the kernels of this step began, so this does not wait for the previous one.
+        int run = 0, run_d = 0;
+        for (int s0 = 0; s0 < p.num_segments; s0 += 32) {
+            const int sg = s0 + lane;
+            const int n = sg < p.num_segments ? fd_seg_tiles(p, sg) : 0;
+            const int dflag = n > 0 ? 1 : 0;
+            int inc = n, inc_d = dflag;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, inc, o), up_d = __shfl_up_sync(0xffffffffu, inc_d, o);
+                if (lane >= o) { inc += up; inc_d += up_d; }
+            }
+            if (sg < p.num_segments) { tile_pre[sg] = run + inc - n; tile_pre[FD_MAX_SEGS + 1 + sg] = run_d + inc_d - dflag; }
+            run += __shfl_sync(0xffffffffu, inc, 31);
+            run_d += __shfl_sync(0xffffffffu, inc_d, 31);
+        }
+        if (lane == 0) { tile_pre[p.num_segments] = run; tile_pre[FD_MAX_SEGS + 1 + p.num_segments] = run_d; }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -784,18 +938,20 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         // ---------------- TMA producer: lane = page of the key tile; runs ahead across items ----------------
         const int ps = p.page_size, pages_per_tile = FA_BN / ps;
         const unsigned page_bytes = (unsigned)ps * 128u;
-        int t = 0, it = (int)blockIdx.x - (int)gridDim.x;
+        int t = 0, newest_seen = 0;
+        FdCursor cur;
+        fd_begin(p, tile_pre, cur);
         FdItem w;
         bool ok = true;
-        while (ok && !*failed && fd_next(p, it, w)) {
+        while (ok && !*failed && fd_next(p, tile_pre, cur, w)) {
             const int* table = p.block_table + (size_t)p.seg_slot[w.seg] * p.bt_stride;
             for (int j = 0; j < w.ntiles; ++j, ++t) {
                 const int st = t % STAGES, use = t / STAGES;
-                if (p.fuse && j == w.ntiles - 1 && w.split == w.nsplits - 1) {
-                    // the tile about to be requested holds the newest position: its key and value are written first,
-                    // by this warp, and made visible to the TMA unit (proxy fence by the writers, then the warp meets)
-                    fd_write_new_token<D>(p, w, table, lane);
-                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                if (p.fuse && j == w.ntiles - 1 && w.newest) {
+                    // the tile about to be requested holds the newest position: the writer warp must have put its key
+                    // and value into the page (and made them visible to the TMA unit) first
+                    ++newest_seen;
+                    if (!fd_wait_count(tokens_written, newest_seen, (8u << 24) | t, failed)) { ok = false; break; }
                     __syncwarp();
                 }
                 const int key = w.kb + j * FA_BN + lane * ps;
@@ -822,7 +978,9 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             // S^T: M 128 keys x N 16 heads, both K-major.  O^T: M 128 (head dimension) x N 16, A (values) MN-major.
             const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
             const unsigned idesc_pv = idesc_s | (1u << 15);
-            int t = 0, ic = 0, it = (int)blockIdx.x - (int)gridDim.x;
+            int t = 0, ic = 0;
+            FdCursor cur;
+            fd_begin(p, tile_pre, cur);
             FdItem w;
             bool ok = true;
             auto issue_s = [&](int tt, int qbuf) -> bool {        // scores of tile tt into buffer tt & 1
@@ -840,7 +998,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 fa_commit(&s_full[tt & 1]);
                 return true;
             };
-            while (ok && !*failed && fd_next(p, it, w)) {
+            while (ok && !*failed && fd_next(p, tile_pre, cur, w)) {
                 if (!fa_mbar_wait(&q_ready[ic & 1], (ic >> 1) & 1, (3u << 24) | ic, failed)) break;
                 const int qbuf = ic & 1;
                 ++ic;
@@ -859,6 +1017,24 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     fa_commit(pv_done);
                     fa_commit(&empty[st]);        // keys and values of this stage are no longer read
                 }
+            }
+        }
+    } else if (warp == 6) {
+        // ---------------- writer of the new tokens (fused mode): ahead of the producer, pair by pair ----------------
+        if (p.fuse) {
+            FdCursor cur;
+            fd_begin(p, tile_pre, cur);
+            FdItem w;
+            int done = 0;
+            while (!*failed && fd_next(p, tile_pre, cur, w)) {
+                if (!w.newest) continue;
+                const int* table = p.block_table + (size_t)p.seg_slot[w.seg] * p.bt_stride;
+                fd_write_new_token<D>(p, w, table, lane);
+                // visible to the TMA unit (proxy fence by the writers), then the warp meets and says so
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __syncwarp();
+                ++done;
+                if (lane == 0) fd_set_count(tokens_written, done);
             }
         }
     } else {
@@ -938,12 +1114,14 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             if (lane == 0) fa_mbar_arrive(&q_ready[buf]);
         };
         FdItem w, wn;
-        int it = (int)blockIdx.x - (int)gridDim.x;
-        bool have = fd_next(p, it, w);
+        FdItem cut[2];               // pieces of cut pairs that this CTA has left in the scratch
+        int cut_tok[2], ncut = 0;
+        FdCursor cur;
+        fd_begin(p, tile_pre, cur);
+        bool have = fd_next(p, tile_pre, cur, w);
         if (have) { fetch_q(w); finish_q(w); store_q(0); }
         while (have) {
-            int it_next = it;
-            const bool have_next = fd_next(p, it_next, wn);
+            const bool have_next = fd_next(p, tile_pre, cur, wn);
             if (have_next) fetch_q(wn);                    // lands while this item's first tile is worked on
             const int tok = p.seg_off[w.seg];
             float m_run[GP], l_thr[GP];
@@ -1000,7 +1178,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 if (lane == 0) fa_mbar_arrive(p_ready);
                 if (j == 0 && have_next) { finish_q(wn); store_q((ic + 1) & 1); }     // the next item's queries, fetched above
             }
-            // ---------------- the item's result ----------------
+            // ---------------- the piece's result ----------------
             alive = alive && fa_mbar_wait(pv_done, (t - 1) & 1, (7u << 24) | t, failed);
             fa_fence_after();
             float o[GP];
@@ -1014,26 +1192,57 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             }
             fd_softmax_sync();
             if (alive) {
+                const size_t ws_row = ((size_t)blockIdx.x * 2 + w.slot) * 16;
 #pragma unroll
                 for (int g = 0; g < GP; ++g) {
                     if (g < G) {
                         const float4 q4 = *reinterpret_cast<const float4*>(xsum + g * 4);
                         const float l = (q4.x + q4.y) + (q4.z + q4.w);
-                        const size_t row = (size_t)tok * p.nq + (size_t)w.kvh * G + g;
-                        if (w.nsplits == 1) {
+                        if (w.whole) {
+                            const size_t row = (size_t)tok * p.nq + (size_t)w.kvh * G + g;
                             if (tid < D) p.out[row * D + tid] = __float2bfloat16_rn(l > 0.0f ? o[g] / l : 0.0f);
                         } else {
-                            if (tid < D) p.part_acc[(row * p.max_splits + w.split) * D + tid] = o[g];
+                            if (tid < D) p.ws_acc[(ws_row + g) * D + tid] = o[g];
                             if (tid == 0) {
-                                p.part_ml[(row * p.max_splits + w.split) * 2] = m_run[g];
-                                p.part_ml[(row * p.max_splits + w.split) * 2 + 1] = l;
+                                p.ws_ml[(ws_row + g) * 2] = m_run[g];
+                                p.ws_ml[(ws_row + g) * 2 + 1] = l;
                             }
                         }
                     }
                 }
             }
-            fd_softmax_sync();            // xsum is read before the next item overwrites it
-            w = wn; have = have_next; it = it_next; ++ic;
+            if (!w.whole) {          // at most two per span: one that began before it, one that goes on behind it
+                if (ncut == 0) { cut[0] = w; cut_tok[0] = tok; } else { cut[1] = w; cut_tok[1] = tok; }
+                ++ncut;
+            }
+            fd_softmax_sync();            // xsum is read before the next piece overwrites it
+            w = wn; have = have_next; ++ic;
+        }
+        // The span is done.  Its pieces of cut pairs are reported (writes, fence, then the count), and whoever reports
+        // a pair's last piece adds them all up.  One thread takes the decisions for the four warps.
+        if (ncut > 0) {
+            __threadfence();
+            fd_softmax_sync();
+            if (tid == 0) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (i >= ncut) break;
+                    int last = 0;
+                    if (alive) {
+                        const unsigned before = atomicAdd(p.ws_count + cut[i].cta_first, 1u);
+                        last = (before + 1u == (unsigned)cut[i].pieces) ? 1 : 0;
+                        if (last) p.ws_count[cut[i].cta_first] = 0u;         // ready for the next launch
+                    }
+                    merge_here[i] = last;
+                }
+            }
+            fd_softmax_sync();
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                if (i < ncut && merge_here[i]) {
+                    __threadfence();
+                    fd_merge<D, GP>(p, cut[i], cut_tok[i], tid, G);
+                }
         }
     }
     // ---------------- common exit ----------------
@@ -1145,9 +1354,10 @@ PI_EXPORT int pi_attention_decode_tcgen05_supported(int page_size, int group) {
     return (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) && group >= 1 && group <= 16;
 }
 
-// Segments of one token only (the others are skipped).  Requests whose keys are cut into more than one range
-// leave (max, sum, accumulator) per range in part_ml / part_acc for attn_merge_kernel; split_keys must be a
-// multiple of 128.
+// Segments of one token only (the others are skipped).  The workspace serves the pairs that are cut between CTAs:
+// ws_acc [ws_ctas * 2 * 16 * D] and ws_ml [ws_ctas * 2 * 16 * 2] floats need no initial contents; ws_count [ws_ctas]
+// must be zero before the first launch and is left zero by every launch that ends without a failed wait.  Launches
+// that share a workspace must not overlap.  The kernel runs on min(SMs, ws_ctas) CTAs.
 // what the fused form needs beside the arguments of pi_attention_decode_tcgen05
 struct FdFusion {
     int fuse;
@@ -1158,17 +1368,19 @@ struct FdFusion {
 
 static int fd_launch(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
                      const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
-                     const int* seg_start, const int* seg_len, void* out, float* part_acc, float* part_ml,
-                     int max_splits, int split_keys, int num_segments, int nq, int nkv, int page_size,
+                     const int* seg_start, const int* seg_len, void* out, float* ws_acc, float* ws_ml,
+                     unsigned* ws_count, int ws_ctas, int span_min, int pair_cost, int num_segments, int nq, int nkv, int page_size,
                      int window, float scale, const FdFusion& fusion, cudaStream_t stream) {
     if (num_segments <= 0) return 0;
     if (!(scale > 0.0f)) return pi_refuse("pi_attention_decode_tcgen05: the score scale must be positive");
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) return pi_refuse("pi_attention_decode_tcgen05: nq=%d must be a positive multiple of nkv=%d", nq, nkv);
     if (!pi_attention_decode_tcgen05_supported(page_size, nq / nkv))
         return pi_refuse("pi_attention_decode_tcgen05: page size %d must be 8, 16, 32 or 64 and the group (%d) at most 16", page_size, nq / nkv);
-    if (split_keys <= 0 || split_keys % FA_BN != 0) return pi_refuse("pi_attention_decode_tcgen05: split_keys=%d must be a positive multiple of %d", split_keys, FA_BN);
-    if (max_splits < 1) return pi_refuse("pi_attention_decode_tcgen05: max_splits=%d must be at least 1", max_splits);
-    if (max_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return pi_refuse("pi_attention_decode_tcgen05: scratch for %d key ranges is missing", max_splits);
+    if (num_segments > FD_MAX_SEGS) return pi_refuse("pi_attention_decode_tcgen05: %d segments; this kernel takes at most %d", num_segments, FD_MAX_SEGS);
+    if (ws_ctas < 1 || ws_acc == nullptr || ws_ml == nullptr || ws_count == nullptr)
+        return pi_refuse("pi_attention_decode_tcgen05: the workspace (for %d CTAs) is missing", ws_ctas);
+    if (span_min < 1 || pair_cost < 0 || pair_cost > 64)
+        return pi_refuse("pi_attention_decode_tcgen05: span_min=%d must be at least 1 and pair_cost=%d between 0 and 64", span_min, pair_cost);
     if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)kcache & 127) || ((uintptr_t)vcache & 127))
         return pi_refuse("pi_attention_decode_tcgen05: q must be 16-byte aligned with a stride that is a multiple of 8, pages 128-byte aligned");
     CUtensorMap mk, mv;
@@ -1177,22 +1389,24 @@ static int fd_launch(const void* q, int q_stride, const void* kcache, const void
     if (rc) return rc;
     rc = fa_make_map(&mv, vcache, rows, page_size);
     if (rc) return rc;
-    const long long items = (long long)num_segments * nkv * max_splits;
-    if (items > 2147483647LL) return pi_refuse("pi_attention_decode_tcgen05: %lld items are beyond the limit", items);
+    // the longest sequence of tiles the 32-bit cursors may meet: every segment at the last position a block table row holds
+    const long long tiles_bound = (long long)num_segments * nkv * (((long long)bt_stride * page_size + FA_BN - 1) / FA_BN + 1 + pair_cost);
+    if (tiles_bound > 2147483647LL / 2) return pi_refuse("pi_attention_decode_tcgen05: up to %lld key tiles are beyond the limit", tiles_bound);
     FdParams p;
     p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.bt_stride = bt_stride;
     p.seg_off = seg_off; p.seg_slot = seg_slot; p.seg_start = seg_start; p.seg_len = seg_len;
-    p.out = (bf16*)out; p.part_acc = part_acc; p.part_ml = part_ml; p.max_splits = max_splits;
+    p.out = (bf16*)out; p.ws_acc = ws_acc; p.ws_ml = ws_ml; p.ws_count = ws_count; p.span_min = span_min; p.pair_cost = pair_cost;
     p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.page_size = page_size; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.num_segments = num_segments; p.split_keys = split_keys; p.num_items = (int)items;
+    p.num_segments = num_segments;
     p.fuse = fusion.fuse; p.kpool = (bf16*)kcache; p.vpool = (bf16*)vcache;
     p.qw = fusion.qw; p.kw = fusion.kw; p.w_f32 = fusion.w_f32; p.eps = fusion.eps;
     p.cos_t = fusion.cos_t; p.sin_t = fusion.sin_t; p.rot_pairs = fusion.rot_pairs; p.error_count = fusion.error_count;
     static int sms = 0;
     static bool configured = false;
     constexpr unsigned tile_bytes = (PI_HEAD_DIM / 64) * 128 * 128;
-    const size_t smem = (size_t)FD_STAGES * 2 * tile_bytes + 6 * 16 * 128 + (2 * 4 * 16 + 4 * 16) * 4 + (2 * FD_STAGES + 6) * 8 + 16 + 1024;
+    const size_t smem = (size_t)FD_STAGES * 2 * tile_bytes + 6 * 16 * 128 + (2 * 4 * 16 + 4 * 16) * 4 + (2 * FD_STAGES + 6) * 8 + 32 +
+                        2 * (FD_MAX_SEGS + 1) * 4 + 1024;
     if (!configured) {
         int dev = 0;
         cudaError_t err = cudaGetDevice(&dev);
@@ -1206,7 +1420,7 @@ static int fd_launch(const void* q, int q_stride, const void* kcache, const void
         }
         configured = true;
     }
-    const unsigned ctas = (unsigned)(items < sms ? items : sms);
+    const unsigned ctas = (unsigned)(ws_ctas < sms ? ws_ctas : sms);
     if (p.group <= 4) pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 4>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
     else if (p.group <= 8) pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 8>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
     else pi_launch(attn_decode_tcgen05_kernel<PI_HEAD_DIM, 16>, dim3(ctas), dim3(FD_THREADS), smem, stream, mk, mv, p);
@@ -1215,12 +1429,12 @@ static int fd_launch(const void* q, int q_stride, const void* kcache, const void
 
 PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const void* kcache, const void* vcache, long long num_pages,
                                           const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
-                                          const int* seg_start, const int* seg_len, void* out, float* part_acc, float* part_ml,
-                                          int max_splits, int split_keys, int num_segments, int nq, int nkv, int page_size,
-                                          int window, float scale, cudaStream_t stream) {
+                                          const int* seg_start, const int* seg_len, void* out, float* ws_acc, float* ws_ml,
+                                          unsigned* ws_count, int ws_ctas, int span_min, int pair_cost, int num_segments, int nq, int nkv,
+                                          int page_size, int window, float scale, cudaStream_t stream) {
     const FdFusion none = {0, nullptr, nullptr, 0, 0.0f, nullptr, nullptr, 0, nullptr};
     return fd_launch(q, q_stride, kcache, vcache, num_pages, block_table, bt_stride, seg_off, seg_slot, seg_start, seg_len, out,
-                     part_acc, part_ml, max_splits, split_keys, num_segments, nq, nkv, page_size, window, scale, none, stream);
+                     ws_acc, ws_ml, ws_count, ws_ctas, span_min, pair_cost, num_segments, nq, nkv, page_size, window, scale, none, stream);
 }
 
 // The same for a step of single tokens straight from the q/k/v product: `qkv` [T, q_stride] holds nq query heads,
@@ -1231,9 +1445,9 @@ PI_EXPORT int pi_attention_decode_tcgen05(const void* q, int q_stride, const voi
 // is missing is counted in *error_count and not written.  Every segment must be a single token.
 PI_EXPORT int pi_attention_decode_tcgen05_fused(const void* qkv, int q_stride, void* kcache, void* vcache, long long num_pages,
                                                 const int* block_table, int bt_stride, const int* seg_off, const int* seg_slot,
-                                                const int* seg_start, const int* seg_len, void* out, float* part_acc,
-                                                float* part_ml, int max_splits, int split_keys, int num_segments, int nq,
-                                                int nkv, int page_size, int window, float scale, const void* q_weight,
+                                                const int* seg_start, const int* seg_len, void* out, float* ws_acc,
+                                                float* ws_ml, unsigned* ws_count, int ws_ctas, int span_min, int pair_cost, int num_segments,
+                                                int nq, int nkv, int page_size, int window, float scale, const void* q_weight,
                                                 const void* k_weight, int weight_dtype, float eps, const float* cos_t,
                                                 const float* sin_t, int rot_pairs, int* error_count, cudaStream_t stream) {
     if ((q_weight == nullptr) != (k_weight == nullptr)) return pi_refuse("pi_attention_decode_tcgen05_fused: give both norm weights or none");
@@ -1245,7 +1459,7 @@ PI_EXPORT int pi_attention_decode_tcgen05_fused(const void* qkv, int q_stride, v
     if (q_stride < (nq + 2 * nkv) * PI_HEAD_DIM) return pi_refuse("pi_attention_decode_tcgen05_fused: rows of %d elements cannot hold %d + 2 x %d heads", q_stride, nq, nkv);
     const FdFusion fusion = {1, q_weight, k_weight, weight_dtype == PI_F32 ? 1 : 0, eps, cos_t, sin_t, rot_pairs, error_count};
     return fd_launch(qkv, q_stride, kcache, vcache, num_pages, block_table, bt_stride, seg_off, seg_slot, seg_start, seg_len, out,
-                     part_acc, part_ml, max_splits, split_keys, num_segments, nq, nkv, page_size, window, scale, fusion, stream);
+                     ws_acc, ws_ml, ws_count, ws_ctas, span_min, pair_cost, num_segments, nq, nkv, page_size, window, scale, fusion, stream);
 }
 
 #else   // head sizes this kernel does not take

@@ -53,6 +53,8 @@ class AttentionScratch:
     prompt_splits: int = 1
     prompt_acc: torch.Tensor | None = None
     prompt_ml: torch.Tensor | None = None
+    # single tokens on the tcgen05 decode kernel: its workspace (the key ranges above are then not used)
+    decode_ws: "ops.DecodeWorkspace | None" = None
 
 
 class StepContext:
@@ -173,13 +175,30 @@ class StepContext:
         keys, values = group.kv(cache_index)
         return CacheView(keys, values, group.device_table, cm.page_size, state)
 
+    def _decode_workspace(self, head_dim: int):
+        """One workspace per head size for all layers and steps of a runtime: they run one after the other on one stream."""
+        held = getattr(self.runtime, "decode_workspaces", None)
+        if held is None:
+            held = {}
+            try:
+                self.runtime.decode_workspaces = held
+            except AttributeError:
+                pass
+        ws = held.get(head_dim)
+        if ws is None:
+            ws = held[head_dim] = ops.attention_decode_workspace(head_dim, self.device)
+        return ws
+
     def attention_scratch(self, num_heads: int, head_dim: int, window, num_kv_heads: int = 1) -> AttentionScratch:
-        """Scratch of the split decode attention: partial outputs and (max, sum) pairs per key range."""
+        """Scratch of the decode attention: the workspace of the tcgen05 kernel, or for the mma.sync kernel partial
+        outputs and (max, sum) pairs per key range; and the shares of the prompt kernel."""
         key = (num_heads, head_dim, window)
         sc = self._scratch.get(key)
         if sc is None:
             if not self.has_decode:
                 sc = AttentionScratch(1, None, None)
+            elif ops.decode_on_tcgen05(head_dim, self.cache_manager.page_size, num_heads // max(num_kv_heads, 1), self.act_dtype):
+                sc = AttentionScratch(1, None, None, decode_ws=self._decode_workspace(head_dim))
             else:
                 split_keys = (self.split_keys or {}).get((num_kv_heads, head_dim)) or ops.choose_split_keys(
                     len(self.decode_starts), num_kv_heads, self.decode_pos_max, head_dim)

@@ -1,8 +1,8 @@
 """Decode steps as CUDA graphs.
 
 A step that holds only single decoded tokens launches a few hundred small kernels; at batch 1 their
-launch cost exceeds their run time.  Such a step is captured once per (number of requests, bound on the
-number of key ranges) and replayed: the metadata buffer, the block tables and the output live at fixed
+launch cost exceeds their run time.  Such a step is captured once per (number of requests, and for layers
+whose decode attention cuts keys into ranges a bound on their number) and replayed: the metadata buffer, the block tables and the output live at fixed
 addresses and are refilled in place before each replay.  The captured work is exactly what the eager
 step runs (same model code, same kernels).  The reference launches everything eagerly on the null
 stream (``src/ops/rope.cpp:231``, ``src/ops/matmul.cpp:115``).
@@ -10,6 +10,7 @@ stream (``src/ops/rope.cpp:231``, ``src/ops/matmul.cpp:115``).
 from __future__ import annotations
 
 import gc
+import time
 
 import torch
 
@@ -64,6 +65,7 @@ class DecodeGraph:
                 raise ValueError("tokens_from must hold one int32 id per request of the step")
             self.ctx.tokens.copy_(tokens_from.reshape(-1))
         if self.graph is None:
+            t0 = time.perf_counter()
             model = self.runner.model
             # Once eagerly (library initialisation, kernel attributes), then capture the same work.  The eager run and
             # the first replay both compute this step: page writes are idempotent, and fixed-size per-request state
@@ -89,6 +91,7 @@ class DecodeGraph:
                     gc.enable()
             self.launches_per_replay = ops.kernels.LAUNCHES - before
             self.graph = graph
+            self.record_seconds = time.perf_counter() - t0
         self.graph.replay()
         ops.kernels.count_launches(self.launches_per_replay)
         return self.logits
@@ -101,6 +104,8 @@ class DecodeGraphs:
         self.runner = runner
         self.max_graphs = max_graphs
         self.graphs: dict = {}
+        self.recordings = 0            # steps recorded so far, and the host time that took
+        self.record_seconds = 0.0
 
     def eligible(self, segments) -> bool:
         """A step of single tokens, each wanting its logits, of a model whose parts all allow recording
@@ -110,7 +115,15 @@ class DecodeGraphs:
         return all(len(s.tokens) == 1 and list(s.want) == [0] for s in segments)
 
     def run(self, segments, tokens_from=None) -> torch.Tensor:
-        specs = {cs for cs in self.runner.model.cache_specs() if cs is not None}
+        # kinds of layers whose decode attention works on key ranges (parts that do not say are taken to)
+        page_size, act_dtype = self.runner.cache.page_size, self.runner.runtime.act_dtype
+        specs = set()
+        for part in self.runner.model.all_parts():
+            spec_of = getattr(part, "cache_spec", None)
+            cs = spec_of() if spec_of is not None else None
+            uses = getattr(part, "uses_key_ranges", None)
+            if cs is not None and (uses is None or uses(page_size, act_dtype)):
+                specs.add(cs)
         starts = [s.start for s in segments]
         pos_max = max(starts)
         # keys per range for every kind of layer (kv heads, head size), and one bound on the ranges for the whole
@@ -128,4 +141,9 @@ class DecodeGraphs:
                 self.graphs.pop(next(iter(self.graphs)))
             g = DecodeGraph(self.runner, *key)
             self.graphs[key] = g
-        return g.run(segments, tokens_from)
+        fresh = g.graph is None
+        logits = g.run(segments, tokens_from)
+        if fresh:
+            self.recordings += 1
+            self.record_seconds += g.record_seconds
+        return logits

@@ -251,20 +251,12 @@ def sm_count() -> int:
 
 
 def choose_split_keys(num_decode: int, num_kv_heads: int, max_pos: int, head_dim: int | None = None) -> int:
-    """Keys per range of the split decode attention (from measurements on B200).
-    The persistent tcgen05 kernel (head sizes 64 / 128) wants about one item per SM and as few ranges as that
-    allows: the longest range that still gives 120 items.  The mma.sync kernel wants several CTAs per SM: short
-    ranges for a small batch, long ones (less start-up cost per byte) for a large one."""
+    """Keys per range of the split decode attention of the mma.sync kernel (from measurements on B200): it wants
+    several CTAs per SM, so short ranges for a small batch and long ones (less start-up cost per byte) for a large one.
+    (The tcgen05 decode kernel cuts the keys of a step into equal spans by itself.)"""
     forced = os.environ.get("PULSE_SPLIT_KEYS")
     if forced:
         return int(forced)
-    if TCGEN05_DECODE and TCGEN05_ATTENTION and head_dim in (64, 128):
-        pairs = num_decode * max(num_kv_heads, 1)
-        items = sm_count() * 120 // 148          # about four fifths of the SMs busy before ranges get longer
-        for keys in (2048, 1024, 512):
-            if pairs * (max_pos + 1) >= items * keys:
-                return keys
-        return SPLIT_KEYS
     tiles = (max_pos + 256) // 256
     ctas = num_decode * max(num_kv_heads, 1) * tiles
     sms = sm_count()
@@ -306,6 +298,28 @@ TCGEN05_DECODE = os.environ.get("PULSE_TCGEN05_DECODE", "1") != "0"     # single
 
 def attention_decode_tcgen05_usable(head_dim: int, page_size: int, group: int) -> bool:
     return TCGEN05_ATTENTION and head_dim in (64, 128) and page_size in (8, 16, 32, 64) and 1 <= group <= 16
+
+
+DECODE_SPAN_MIN = int(os.environ.get("PULSE_DECODE_SPAN_MIN", "4"))     # shortest span of a CTA of the decode kernel, in units (key tiles + costs)
+DECODE_PAIR_COST = int(os.environ.get("PULSE_DECODE_PAIR_COST", "2"))    # units a (request, kv head) pair counts for beside its key tiles
+
+
+class DecodeWorkspace:
+    """What the tcgen05 decode attention kernel keeps between its CTAs: the partial results of (request, kv head) pairs
+    whose keys were cut between CTAs, two slots of 16 heads per CTA, and a counter per CTA that says how many pieces of
+    the pair that begins there have been delivered.  Its size does not depend on the batch or on the context.  The
+    counters are zero between launches; launches that share a workspace must not overlap (one stream)."""
+
+    def __init__(self, head_dim: int, device):
+        self.ctas = sm_count()
+        self.head_dim = head_dim
+        self.acc = torch.empty(self.ctas * 2 * 16 * head_dim, dtype=torch.float32, device=device)
+        self.ml = torch.empty(self.ctas * 2 * 16 * 2, dtype=torch.float32, device=device)
+        self.count = torch.zeros(self.ctas, dtype=torch.int32, device=device)
+
+
+def attention_decode_workspace(head_dim: int, device) -> DecodeWorkspace:
+    return DecodeWorkspace(head_dim, device)
 
 
 def attention_tcgen05_usable(head_dim: int, page_size: int) -> bool:
@@ -382,13 +396,15 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
                   window: int | None, scale: float, out: torch.Tensor | None = None,
                   split_keys: int = SPLIT_KEYS, prefetch: torch.Tensor | None = None,
                   prompt_on_tcgen05: bool = True, decode_on_tcgen05: bool | None = None, prompt_splits: int = 1,
-                  prompt_acc: torch.Tensor | None = None, prompt_ml: torch.Tensor | None = None) -> torch.Tensor:
+                  prompt_acc: torch.Tensor | None = None, prompt_ml: torch.Tensor | None = None,
+                  decode_ws: DecodeWorkspace | None = None) -> torch.Tensor:
     """Tensor-core paged attention for bfloat16 over request segments.  Prompt portions (segments of several tokens)
     and single tokens are separate kernels: for head sizes 64 / 128 the tcgen05 kernels of csrc/attention_tcgen05.cu
-    (``prompt_on_tcgen05`` / ``decode_on_tcgen05``; the ranges of a split decode are combined by the merge kernel
-    of csrc/attention_mma.cu), otherwise - and for sizes those do not take - the mma.sync kernels of
-    csrc/attention_mma.cu.  ``prompt_splits`` / ``prompt_acc`` / ``prompt_ml``: key splitting of the tcgen05 prompt
-    kernel (see ``attention_tcgen05``)."""
+    (``prompt_on_tcgen05`` / ``decode_on_tcgen05``; the decode kernel cuts the keys of the step into equal spans by
+    itself and wants ``decode_ws``, made here when missing), otherwise - and for sizes those do not take - the
+    mma.sync kernels of csrc/attention_mma.cu with key ranges of ``split_keys`` keys, ``max_splits`` of them at most,
+    in ``part_acc`` / ``part_ml``.  ``prompt_splits`` / ``prompt_acc`` / ``prompt_ml``: key splitting of the tcgen05
+    prompt kernel (see ``attention_tcgen05``)."""
     _need_cuda(q, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml)
     _need_contig(kcache=kcache, vcache=vcache, block_table=block_table)
     if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16:
@@ -405,23 +421,23 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
         if not has_decode:
             return out
         has_prompt = False
-    if has_decode and max_splits > 1:
-        need = num_tokens * nq * max_splits
-        if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:
-            raise KernelError("scratch for the split decode attention is missing or too small")
     decode_mode = 1 if has_decode else 0
-    if (has_decode and decode_on_tcgen05 and attention_decode_tcgen05_usable(head_dim, page_size, nq // nkv)
-            and split_keys % 128 == 0):
-        # single tokens on the persistent tcgen05 kernel; the merge of the key ranges stays with the mma library
+    if has_decode and decode_on_tcgen05 and attention_decode_tcgen05_usable(head_dim, page_size, nq // nkv):
+        # single tokens on the persistent tcgen05 kernel, which also adds up the pieces of requests it has cut
+        ws = _decode_workspace(decode_ws, head_dim, q.device)
         tlib = _lib("attention_tcgen05", head_dim)
         _check(tlib, tlib.pi_attention_decode_tcgen05(
             _p(q), c_int(q_stride), _p(kcache), _p(vcache), ctypes.c_longlong(kcache.shape[0]), _p(block_table),
-            c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), _p(part_acc),
-            _p(part_ml), c_int(max_splits), c_int(split_keys), c_int(num_segments), c_int(nq), c_int(nkv),
+            c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), _p(ws.acc),
+            _p(ws.ml), _p(ws.count), c_int(ws.ctas), c_int(DECODE_SPAN_MIN), c_int(DECODE_PAIR_COST), c_int(num_segments), c_int(nq), c_int(nkv),
             c_int(page_size), c_int(window or 0), c_float(scale), _stream()), "attention_decode_tcgen05")
-        if max_splits <= 1 and not has_prompt:
+        if not has_prompt:
             return out
-        decode_mode = 2 if max_splits > 1 else 0
+        decode_mode = 0
+    if decode_mode and max_splits > 1:
+        need = num_tokens * nq * max_splits
+        if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:
+            raise KernelError("scratch for the split decode attention is missing or too small")
     lib = _lib("attention_mma", head_dim)
     _check(lib, lib.pi_attention_mma_prefetch(
         _p(q), c_int(q_stride), _p(kcache), _p(vcache), _p(block_table), c_int(block_table.shape[1]), _p(seg_off),
@@ -436,26 +452,39 @@ def attention_mma(q: torch.Tensor, q_stride: int, kcache, vcache, block_table, s
 FUSE_ROPE = os.environ.get("PULSE_FUSE_ROPE", "1") != "0"     # steps of single tokens: norm, rotation and page write inside the attention kernel
 
 
-def attention_decode_fused_usable(head_dim: int, page_size: int, group: int, split_keys: int, adjacent_pairs: bool,
+def _decode_workspace(ws: DecodeWorkspace | None, head_dim: int, device) -> DecodeWorkspace:
+    if ws is None:
+        return DecodeWorkspace(head_dim, device)
+    if ws.head_dim < head_dim or ws.acc.device != device:
+        raise KernelError(f"the decode workspace was made for head size {ws.head_dim} on {ws.acc.device}")
+    return ws
+
+
+def decode_on_tcgen05(head_dim: int, page_size: int, group: int, act_dtype: torch.dtype) -> bool:
+    """Whether single tokens of such a layer go to the tcgen05 decode kernel (which cuts the keys by itself) rather
+    than to the mma.sync kernel with its key ranges."""
+    return TCGEN05_DECODE and act_dtype == torch.bfloat16 and attention_decode_tcgen05_usable(head_dim, page_size, group)
+
+
+def attention_decode_fused_usable(head_dim: int, page_size: int, group: int, adjacent_pairs: bool,
                                   act_dtype: torch.dtype) -> bool:
     """Whether a step that holds single tokens only can leave per-head norm, rotation and the page write of the new
     keys and values to the tcgen05 decode attention kernel (``attention_decode_fused``)."""
-    return (FUSE_ROPE and TCGEN05_DECODE and act_dtype == torch.bfloat16 and adjacent_pairs and split_keys % 128 == 0
-            and attention_decode_tcgen05_usable(head_dim, page_size, group))
+    return FUSE_ROPE and adjacent_pairs and decode_on_tcgen05(head_dim, page_size, group, act_dtype)
 
 
-def attention_decode_fused(qkv: torch.Tensor, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg,
-                           num_segments: int, max_splits: int, part_acc, part_ml, nq: int, nkv: int, head_dim: int,
-                           page_size: int, window: int | None, scale: float, q_weight, k_weight, eps: float, cos, sin,
-                           error_count: torch.Tensor, split_keys: int = SPLIT_KEYS, out: torch.Tensor | None = None,
-                           prefetch: torch.Tensor | None = None) -> torch.Tensor:
+def attention_decode_fused(qkv: torch.Tensor, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len,
+                           num_segments: int, nq: int, nkv: int, head_dim: int, page_size: int, window: int | None,
+                           scale: float, q_weight, k_weight, eps: float, cos, sin, error_count: torch.Tensor,
+                           workspace: DecodeWorkspace | None = None, out: torch.Tensor | None = None,
+                           span_min: int | None = None, pair_cost: int | None = None) -> torch.Tensor:
     """A step of single tokens, straight from the q/k/v product: ``qkv`` [T, (nq + 2 nkv) d] raw.  The tcgen05 decode
-    kernel normalises and rotates the queries as it loads them, and writes each token's (normalised, rotated) key
-    and its value into their page before it reads that page; the ranges of a split request are then merged as in
-    ``attention_mma``.  ``q_weight``/``k_weight`` None: no per-head norm; ``cos``/``sin`` None: no rotation (pairs are
-    adjacent elements).  Returns [T, nq * d]."""
-    _need_cuda(qkv, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, token_seg, part_acc, part_ml,
-               q_weight, k_weight, cos, sin, error_count)
+    kernel normalises and rotates the queries as it loads them, writes each token's (normalised, rotated) key and its
+    value into their page before it reads that page, and adds up the pieces of the requests whose keys it has cut
+    between CTAs (``workspace``; made here when missing).  ``q_weight``/``k_weight`` None: no per-head norm;
+    ``cos``/``sin`` None: no rotation (pairs are adjacent elements).  Returns [T, nq * d]."""
+    _need_cuda(qkv, kcache, vcache, block_table, seg_off, seg_slot, seg_start, seg_len, q_weight, k_weight, cos, sin,
+               error_count)
     _need_contig(qkv=qkv, kcache=kcache, vcache=vcache, block_table=block_table, cos=cos, sin=sin)
     T, width = qkv.shape
     if qkv.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or vcache.dtype != torch.bfloat16:
@@ -471,26 +500,18 @@ def attention_decode_fused(qkv: torch.Tensor, kcache, vcache, block_table, seg_o
     rot_pairs = 0 if cos is None else cos.shape[1]
     if cos is not None and (cos.shape != (T, rot_pairs) or sin.shape != cos.shape or cos.dtype != torch.float32):
         raise KernelError("rotation tables must be float32 [T, pairs]")
-    if max_splits > 1:
-        need = T * nq * max_splits
-        if part_acc is None or part_acc.numel() < need * head_dim or part_ml.numel() < need * 2:
-            raise KernelError("scratch for the split decode attention is missing or too small")
+    ws = _decode_workspace(workspace, head_dim, qkv.device)
     if out is None:
         out = torch.empty((T, nq * head_dim), dtype=qkv.dtype, device=qkv.device)
     tlib = _lib("attention_tcgen05", head_dim)
     _check(tlib, tlib.pi_attention_decode_tcgen05_fused(
         _p(qkv), c_int(width), _p(kcache), _p(vcache), ctypes.c_longlong(kcache.shape[0]), _p(block_table),
-        c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), _p(part_acc), _p(part_ml),
-        c_int(max_splits), c_int(split_keys), c_int(num_segments), c_int(nq), c_int(nkv), c_int(page_size), c_int(window or 0),
-        c_float(scale), _p(q_weight), _p(k_weight), c_int(_code(q_weight.dtype) if has_norm else BF16), c_float(eps), _p(cos),
-        _p(sin), c_int(rot_pairs), _p(error_count), _stream()), "attention_decode_tcgen05_fused")
-    if max_splits > 1:      # the merge of the key ranges stays with the mma library
-        lib = _lib("attention_mma", head_dim)
-        _check(lib, lib.pi_attention_mma_prefetch(
-            _p(qkv), c_int(width), _p(kcache), _p(vcache), _p(block_table), c_int(block_table.shape[1]), _p(seg_off),
-            _p(seg_slot), _p(seg_start), _p(seg_len), _p(token_seg), _p(out), _p(part_acc), _p(part_ml), c_int(max_splits),
-            c_int(split_keys), c_int(T), c_int(num_segments), c_int(1), c_int(0), c_int(2), c_int(nq), c_int(nkv),
-            c_int(page_size), c_int(window or 0), c_float(scale), *_prefetch_args(prefetch), _stream()), "attention merge")
+        c_int(block_table.shape[1]), _p(seg_off), _p(seg_slot), _p(seg_start), _p(seg_len), _p(out), _p(ws.acc), _p(ws.ml),
+        _p(ws.count), c_int(ws.ctas), c_int(span_min or DECODE_SPAN_MIN), c_int(DECODE_PAIR_COST if pair_cost is None else pair_cost),
+        c_int(num_segments), c_int(nq), c_int(nkv),
+        c_int(page_size), c_int(window or 0), c_float(scale), _p(q_weight), _p(k_weight),
+        c_int(_code(q_weight.dtype) if has_norm else BF16), c_float(eps), _p(cos), _p(sin), c_int(rot_pairs), _p(error_count),
+        _stream()), "attention_decode_tcgen05_fused")
     return out
 
 

@@ -54,6 +54,11 @@ class Attention(Mixer):
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def uses_key_ranges(self, page_size: int, act_dtype: torch.dtype) -> bool:
+        """Whether decode steps of this layer cut each request's keys into ranges whose number must be bounded when a
+        step is recorded (the mma.sync decode kernel); the tcgen05 decode kernel divides the step's keys by itself."""
+        return not ops.decode_on_tcgen05(self.head_dim, page_size, self.num_heads // self.num_kv_heads, act_dtype)
+
     def tensor_specs(self) -> dict:
         specs = {"q_proj.weight": TensorSpec((self.q_size, self.hidden_size)),
                  "o_proj.weight": TensorSpec((self.hidden_size, self.q_size))}
@@ -99,14 +104,14 @@ class Attention(Mixer):
         if use_mma and self.writes_cache and ctx.has_decode and not ctx.has_prompt and qkv.is_contiguous():
             # a step of single tokens: per-head norm, rotation and the page write happen inside the attention kernel
             scratch = ctx.attention_scratch(self.num_heads, self.head_dim, self.window, self.num_kv_heads)
-            if ops.attention_decode_fused_usable(self.head_dim, cache.page_size, self.num_heads // self.num_kv_heads,
-                                                 scratch.split_keys, rot["adjacent"] if rot else True, ctx.act_dtype):
+            if scratch.decode_ws is not None and ops.attention_decode_fused_usable(
+                    self.head_dim, cache.page_size, self.num_heads // self.num_kv_heads, rot["adjacent"] if rot else True,
+                    ctx.act_dtype):
                 attn = ops.attention_decode_fused(
                     qkv, cache.keys, cache.values, cache.block_table, ctx.seg_off, ctx.seg_slot, ctx.seg_start, ctx.seg_len,
-                    ctx.token_seg, ctx.num_segments, scratch.max_splits, scratch.acc, scratch.ml, self.num_heads,
-                    self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale, self.q_norm, self.k_norm,
-                    self.norm_eps, rot["cos"] if rot else None, rot["sin"] if rot else None, ctx.error_count,
-                    split_keys=scratch.split_keys, prefetch=ctx.prefetch(getattr(ctx, "upcoming_weights", None)))
+                    ctx.num_segments, self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window,
+                    self.scale, self.q_norm, self.k_norm, self.norm_eps, rot["cos"] if rot else None,
+                    rot["sin"] if rot else None, ctx.error_count, workspace=scratch.decode_ws)
                 return ops.linear(attn, self.o, ctx.act_dtype, residual=residual, next_norm=next_norm)
         ops.qk_norm_rope_write(
             qkv, self.q_norm, self.k_norm, self.norm_eps,
@@ -122,7 +127,8 @@ class Attention(Mixer):
                 ctx.has_decode, scratch.max_splits, scratch.acc, scratch.ml, self.num_heads, self.num_kv_heads,
                 self.head_dim, cache.page_size, self.window, self.scale, split_keys=scratch.split_keys,
                 prefetch=ctx.prefetch(getattr(ctx, "upcoming_weights", None)), prompt_splits=scratch.prompt_splits,
-                prompt_acc=scratch.prompt_acc, prompt_ml=scratch.prompt_ml)
+                prompt_acc=scratch.prompt_acc, prompt_ml=scratch.prompt_ml, decode_ws=scratch.decode_ws,
+                decode_on_tcgen05=scratch.decode_ws is not None)
         else:
             attn = ops.attention_simple(
                 qkv, q_stride, cache.keys, cache.values, cache.block_table, ctx.token_slot, ctx.positions,

@@ -93,6 +93,34 @@ def test_lookahead_gives_the_same_tokens_as_reading_every_step(model_folders):
     assert {r for _, r in results[True]} <= {"eos", "length"}
 
 
+def test_warm_up_records_every_batch_size_once(model_folders):
+    """After ``Engine.warm_up()`` the decode steps of all batch sizes are recorded: a run whose batch shrinks request by
+    request records nothing more, leaves every page free, and gives the tokens of an engine that was not warmed up."""
+    need_gpu()
+    from pulse_infer_b200 import Engine
+    folder, cfg = model_folders["D"], CONFIGS["D"]
+    prompts = [random_tokens(40 + i, n, cfg.vocab_size) for i, n in enumerate((9, 21, 14, 30))]
+    limits = [6, 11, 16, 21]
+    results = {}
+    for warm in (False, True):
+        engine = Engine(folder, dtype="bfloat16", page_size=16, num_pages=40, max_batch_size=4, chunk_size=32)
+        graphs = engine.runner.graphs
+        if warm:
+            assert engine.warm_up() == 4 and graphs.recordings == 4
+            assert engine.warm_up() == 0                                   # nothing left to record
+            assert engine.runner.cache.free_pages() == [40] * len(engine.runner.cache.free_pages())
+        before = graphs.recordings
+        ids = [engine.add_request(p, m, ignore_eos=True) for p, m in zip(prompts, limits)]
+        engine.run_until_complete()
+        results[warm] = [engine.get_result(i) for i in ids]
+        assert (graphs.recordings - before == 0) if warm else (graphs.recordings - before >= 3)
+        engine.runner.check_device_errors()
+        engine.runner.cache.check_invariants()
+    assert results[True] == results[False]
+    no_graphs = Engine(folder, dtype="bfloat16", page_size=16, num_pages=40, max_batch_size=4, use_cuda_graphs=False)
+    assert no_graphs.warm_up() == 0
+
+
 def test_generation_survives_preemption_and_eos(model_folders):
     """So few pages that requests are preempted and recomputed; tokens are the same as with plenty."""
     need_gpu()

@@ -136,7 +136,8 @@ def test_qk_norm_rope_write(dtype, nq, nkv, d, rot, adjacent, page):
     assert int(err.item()) == 2 * nkv
 
 
-def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengths, seed=0, spike=None, prompt_splits=1):
+def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengths, seed=0, spike=None, prompt_splits=1,
+                    decode_ws=None):
     """segs: (slot, start, n) with start + n <= lengths[slot]; queries random; returns max error / scale."""
     kv = PagedKV(lengths, nkv, d, page, dtype, dev, seed=seed)
     meta = segments_to_device(segs, dev)
@@ -170,7 +171,7 @@ def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengt
                                 meta["seg_start"], meta["seg_len"], meta["token_seg"], T, len(segs), max(lens),
                                 any(n > 1 for n in lens), any(n == 1 for n in lens), splits, acc, ml, nq, nkv, d, page,
                                 window, scale, prompt_on_tcgen05=(impl == "tcgen05"), decode_on_tcgen05=(impl == "tcgen05"),
-                                prompt_splits=prompt_splits, prompt_acc=pacc, prompt_ml=pml)
+                                prompt_splits=prompt_splits, prompt_acc=pacc, prompt_ml=pml, decode_ws=decode_ws)
         if impl == "tcgen05":
             if not ops.attention_tcgen05_usable(d, page):
                 pytest.skip("the tcgen05 kernel takes head sizes 64 / 128 and page sizes 8..128")
@@ -271,12 +272,14 @@ def test_attention_tcgen05_long_portions(nq, nkv, d, page, window):
 
 @pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 8), (16, 1, 64, 64), (32, 8, 128, 16), (5, 5, 128, 32), (12, 2, 64, 16)])
 @pytest.mark.parametrize("window", [None, 300])
-@pytest.mark.parametrize("norm,rot", [(True, 1.0), (True, 0.5), (False, 1.0), (True, 0.0)])
-def test_attention_decode_fused_matches_the_separate_kernels(nq, nkv, d, page, window, norm, rot):
+@pytest.mark.parametrize("norm,rot,span_min,pair_cost", [(True, 1.0, 2, 0), (True, 0.5, 1, 1), (False, 1.0, 3, 2), (True, 0.0, 40, 5)])
+def test_attention_decode_fused_matches_the_separate_kernels(nq, nkv, d, page, window, norm, rot, span_min, pair_cost):
     """A step of single tokens with per-head norm, rotation and the page write done inside the tcgen05 decode kernel,
-    against the separate kernels (qk_norm_rope_write, then attention): the same keys and values in the pages (values
-    bitwise, keys to one rounding), untouched pages untouched, the same attention output; requests of 1 to 1,300
-    keys, so that the newest key sits in a first, a middle and a last tile and ranges are split."""
+    against the separate kernels (qk_norm_rope_write, then the mma.sync attention): the same keys and values in the
+    pages (values bitwise, keys to one rounding), untouched pages untouched, the same attention output; requests of 1
+    to 1,300 keys, so that the newest key sits in a first, a middle and a last tile, and spans of at least 1, 2, 3 and
+    40 units with 0 to 5 units of cost per pair, so that requests are cut in different places or not at all.  Both
+    calls share one workspace."""
     dev, ops = need_gpu(), _ops()
     lengths = [1, 17, 128, 129, 700, 1300, 513, 64]
     segs = [(i, n - 1, 1) for i, n in enumerate(lengths)]
@@ -308,14 +311,17 @@ def test_attention_decode_fused_matches_the_separate_kernels(nq, nkv, d, page, w
     acc, ml = scratch()
     want = ops.attention_mma(q1, q1.shape[1], k1, v1, kv.table_dev, meta["seg_off"], meta["seg_slot"], meta["seg_start"],
                              meta["seg_len"], meta["token_seg"], T, T, 1, False, True, splits, acc, ml, nq, nkv, d, page, window,
-                             scale, split_keys=split_keys)
-    # one kernel
+                             scale, split_keys=split_keys, decode_on_tcgen05=False)
+    # one kernel; its workspace starts as NaN: a piece that is read without having been written shows
+    ws = ops.attention_decode_workspace(d, dev)
+    ws.acc.fill_(float("nan")); ws.ml.fill_(float("nan"))
     k2, v2 = kv.kcache.clone(), kv.vcache.clone()
-    acc, ml = scratch()
     got = ops.attention_decode_fused(qkv.clone(), k2, v2, kv.table_dev, meta["seg_off"], meta["seg_slot"], meta["seg_start"],
-                                     meta["seg_len"], meta["token_seg"], T, splits, acc, ml, nq, nkv, d, page, window, scale,
-                                     qw, kw, eps, cos, sin, err2, split_keys=split_keys)
+                                     meta["seg_len"], T, nq, nkv, d, page, window, scale, qw, kw, eps, cos, sin, err2,
+                                     workspace=ws, span_min=span_min, pair_cost=pair_cost)
     assert ops.attention_tcgen05_status(d) == 0 and int(err1.item()) == 0 and int(err2.item()) == 0
+    assert int(ws.count.abs().sum().item()) == 0                          # the counters are left ready for the next launch
+    assert torch.isfinite(got.float()).all()
     assert torch.equal(v2, v1)                                           # values: a copy
     kd = (k2.float() - k1.float()).abs()
     assert float(kd.max()) <= 2 ** -7 * float(k1.float().abs().max())    # keys: the same arithmetic, at most a rounding apart
@@ -327,11 +333,35 @@ def test_attention_decode_fused_matches_the_separate_kernels(nq, nkv, d, page, w
     bad = kv.table_dev.clone()
     bad[5, (lengths[5] - 1) // page] = -1
     k3, v3 = kv.kcache.clone(), kv.vcache.clone()
-    acc, ml = scratch()
     ops.attention_decode_fused(qkv.clone(), k3, v3, bad, meta["seg_off"], meta["seg_slot"], meta["seg_start"], meta["seg_len"],
-                               meta["token_seg"], T, splits, acc, ml, nq, nkv, d, page, window, scale, qw, kw, eps, cos, sin, err2,
-                               split_keys=split_keys)
+                               T, nq, nkv, d, page, window, scale, qw, kw, eps, cos, sin, err2, workspace=ws, span_min=span_min, pair_cost=pair_cost)
     assert int(err2.item()) == nkv and ops.attention_tcgen05_status(d) == 0
+    assert int(ws.count.abs().sum().item()) == 0
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (32, 8, 128, 16), (12, 3, 64, 8), (16, 1, 64, 64), (40, 8, 128, 32)])
+@pytest.mark.parametrize("window", [None, 700])
+@pytest.mark.parametrize("span_min,pair_cost", [(1, 0), (4, 2), (7, 1), (2, 9)])
+def test_attention_decode_spans_of_unequal_requests(nq, nkv, d, page, window, span_min, pair_cost, monkeypatch):
+    """The tcgen05 decode kernel gives every CTA an equal span of the step's key tiles: requests of 3 to 5,000 keys in
+    one step (some inside one span, some cut two or twenty times), against the dense reference.  One key far back in
+    the longest request is made to stand out, so a piece that is dropped or counted twice shows; a prompt portion in
+    the same step is not touched by the decode kernel's spans; three launches share one workspace."""
+    dev, ops = need_gpu(), _ops()
+    monkeypatch.setattr(ops.kernels, "DECODE_SPAN_MIN", span_min)
+    monkeypatch.setattr(ops.kernels, "DECODE_PAIR_COST", pair_cost)
+    lengths = [5000, 3, 129, 1200, 77, 2047, 640, 128, 300, 1]
+    ws = ops.attention_decode_workspace(d, dev)
+    ws.acc.fill_(float("nan")); ws.ml.fill_(float("nan"))
+    decodes = [(i, n - 1, 1) for i, n in enumerate(lengths)]
+    others = [sg for sg in decodes if sg[0] != 8]
+    steps = [decodes, [sg for sg in decodes if sg[0] in (0, 3, 4, 9)], others[:5] + [(8, 100, 200)] + others[5:]]
+    for call, segs in enumerate(steps):
+        spike = (0, 1234 if window is None else 4500, nq - 1)
+        err = _attention_case(ops, dev, torch.bfloat16, "tcgen05", nq, nkv, d, page, window, segs, lengths, seed=call + nq,
+                              spike=spike, decode_ws=ws)
+        assert err < 0.03, (call, err)
+        assert int(ws.count.abs().sum().item()) == 0
 
 
 @pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 8), (4, 1, 64, 128), (32, 8, 128, 16)])
