@@ -286,16 +286,9 @@ def run_ours(args) -> dict:
     build_s = time.time() - t_build
     wbytes = weight_bytes_per_step(cfg)
 
-    prefill_ms = timed_prefill(engine, rng)
-    pf = prefill_flops(cfg, PROMPT)
-
+    # The headline first, on a GPU that has done nothing but the untimed steps that bring the batch to its context;
+    # the prefill and the other batch sizes (batch 64 runs under the power cap) follow.
     points = {}
-    for b in batches:
-        if b == args.batch:
-            continue
-        ms, _, _, _, _ = timed_decode(engine, b, min(args.steps, 32), args.warmup, rng, through_api=False)
-        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
-
     clocks = ClockSampler()
     clocks.start()
     time.sleep(0.3)
@@ -305,6 +298,14 @@ def run_ours(args) -> dict:
     clock_info = clocks.stop(t0, t1)
     points[f"decode_b{args.batch}"] = round(args.batch * 1000.0 / ms, 1)
     e2e_ms, _, _, h2d_e, d2h_e = timed_decode(engine, args.batch, args.steps, args.warmup, rng, through_api=True)
+
+    prefill_ms = timed_prefill(engine, rng)
+    pf = prefill_flops(cfg, PROMPT)
+    for b in batches:
+        if b == args.batch:
+            continue
+        b_ms, _, _, _, _ = timed_decode(engine, b, min(args.steps, 32), args.warmup, rng, through_api=False)
+        points[f"decode_b{b}"] = round(b * 1000.0 / b_ms, 1)
 
     value = args.batch * 1000.0 / ms
     step_bytes = wbytes + kv_bytes(cfg, args.batch, mean_ctx)
