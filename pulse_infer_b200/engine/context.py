@@ -197,7 +197,8 @@ class StepContext:
         if sc is None:
             if not self.has_decode:
                 sc = AttentionScratch(1, None, None)
-            elif ops.decode_on_tcgen05(head_dim, self.cache_manager.page_size, num_heads // max(num_kv_heads, 1), self.act_dtype):
+            elif ops.decode_on_tcgen05(head_dim, self.cache_manager.page_size, num_heads // max(num_kv_heads, 1), self.act_dtype,
+                                       self.num_segments):
                 sc = AttentionScratch(1, None, None, decode_ws=self._decode_workspace(head_dim))
             else:
                 split_keys = (self.split_keys or {}).get((num_kv_heads, head_dim)) or ops.choose_split_keys(

@@ -110,7 +110,7 @@ class DecodeGraphs:
     def eligible(self, segments) -> bool:
         """A step of single tokens, each wanting its logits, of a model whose parts all allow recording
         (``parts.base.Part.capturable``); everything else is launched kernel by kernel."""
-        if not getattr(self.runner.model, "capturable", False):
+        if not getattr(self.runner.model, "capturable", False) or len(segments) > ops.DECODE_MAX_SEGMENTS:
             return False
         return all(len(s.tokens) == 1 and list(s.want) == [0] for s in segments)
 

@@ -460,10 +460,14 @@ def _decode_workspace(ws: DecodeWorkspace | None, head_dim: int, device) -> Deco
     return ws
 
 
-def decode_on_tcgen05(head_dim: int, page_size: int, group: int, act_dtype: torch.dtype) -> bool:
+DECODE_MAX_SEGMENTS = 1024      # requests per step that the tcgen05 decode kernel takes (FD_MAX_SEGS in csrc/attention_tcgen05.cu)
+
+
+def decode_on_tcgen05(head_dim: int, page_size: int, group: int, act_dtype: torch.dtype, num_segments: int = 0) -> bool:
     """Whether single tokens of such a layer go to the tcgen05 decode kernel (which cuts the keys by itself) rather
-    than to the mma.sync kernel with its key ranges."""
-    return TCGEN05_DECODE and act_dtype == torch.bfloat16 and attention_decode_tcgen05_usable(head_dim, page_size, group)
+    than to the mma.sync kernel with its key ranges; a step of more than DECODE_MAX_SEGMENTS segments does not."""
+    return (TCGEN05_DECODE and act_dtype == torch.bfloat16 and num_segments <= DECODE_MAX_SEGMENTS
+            and attention_decode_tcgen05_usable(head_dim, page_size, group))
 
 
 def attention_decode_fused_usable(head_dim: int, page_size: int, group: int, adjacent_pairs: bool,

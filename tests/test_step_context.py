@@ -49,3 +49,25 @@ def test_step_context_sizes_the_scratch_for_the_widest_request():
     # without a window the highest position decides
     sc = ctx.attention_scratch(num_heads=2, head_dim=32, window=None, num_kv_heads=1)
     assert sc.max_splits == 2        # 512 keys in ranges of 256
+
+
+def test_step_context_gives_the_tcgen05_decode_kernel_its_workspace_up_to_1024_requests():
+    """Head size 128 in bfloat16: single tokens go to the tcgen05 decode kernel, which needs one workspace per runtime
+    (kept across steps) and no key ranges; a step of more requests than that kernel takes falls back to key ranges."""
+    runtime = Runtime(torch.device("cpu"), "bfloat16")
+    for count, spans in ((3, True), (ops.DECODE_MAX_SEGMENTS, True), (ops.DECODE_MAX_SEGMENTS + 1, False)):
+        cache = CacheManager([CacheSpec(2, 128, None)], [None], 16, 64, count, 4096, allocate_pools=False)
+        segs = [Segment(i, [1], [0]) for i in range(count)]
+        for i, s in enumerate(segs):
+            s.slot, s.start = i, 3000 + (i % 7)
+        ctx = StepContext.build(segs, runtime, cache)
+        sc = ctx.attention_scratch(num_heads=8, head_dim=128, window=None, num_kv_heads=2)
+        assert (sc.decode_ws is not None) == spans
+        if spans:
+            assert sc.max_splits == 1 and sc.acc is None
+            assert sc.decode_ws is runtime.decode_workspaces[128]
+            assert int(sc.decode_ws.count.abs().sum()) == 0 and sc.decode_ws.acc.numel() == sc.decode_ws.ctas * 2 * 16 * 128
+            again = StepContext.build(segs, runtime, cache).attention_scratch(8, 128, None, 2)
+            assert again.decode_ws is sc.decode_ws
+        else:
+            assert sc.max_splits == ops.attention_splits_bound([s.start for s in segs], None, sc.split_keys) and sc.acc is not None
