@@ -300,7 +300,7 @@ def attention_decode_tcgen05_usable(head_dim: int, page_size: int, group: int) -
     return TCGEN05_ATTENTION and head_dim in (64, 128) and page_size in (8, 16, 32, 64) and 1 <= group <= 16
 
 
-DECODE_SPAN_MIN = int(os.environ.get("PULSE_DECODE_SPAN_MIN", "4"))     # shortest span of a CTA of the decode kernel, in units (key tiles + costs)
+DECODE_SPAN_MIN = int(os.environ.get("PULSE_DECODE_SPAN_MIN", "2"))     # shortest span of a CTA of the decode kernel, in units (key tiles + costs)
 DECODE_PAIR_COST = int(os.environ.get("PULSE_DECODE_PAIR_COST", "2"))    # units a (request, kv head) pair counts for beside its key tiles
 
 
