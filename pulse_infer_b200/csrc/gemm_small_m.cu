@@ -226,12 +226,19 @@ static void launch_small_m(const void* x, int ldx, const void* W, int ldw, void*
                            int K, int variant, const SmallMFusion& fu, cudaStream_t stream) {
     const int tiles = (N + SM_FEATURES - 1) / SM_FEATURES;
     if (variant == 0) {   // from measurements on B200 at the sizes of 8B- to 32B-class models
-        if (MT == 1) {
-            if (tiles <= 2 * pi_sm_count()) variant = K >= 8192 ? 3 : 1;   // few tiles: deep K wants more warps per tile
-            else if (tiles <= 1000) variant = 2;
-            else variant = 4;                                    // many waves: light CTAs, four per SM
+        const int sms = pi_sm_count();
+        if (tiles > 1000) {
+            variant = MT == 1 ? 4 : 2;                           // many waves: light CTAs, four per SM (one tile of rows)
         } else {
-            variant = tiles <= 2 * pi_sm_count() ? 1 : 2;
+            // A few waves at most: the shape with the fewest waves (a 449th tile behind 444 resident ones costs a whole
+            // second wave), among equals the one with the fewest, heaviest CTAs per SM.
+            const int ctas_per_sm[3] = {2, 3, 4}, shape[3] = {1, 2, 4};
+            int best_waves = 1 << 30;
+            for (int i = 0; i < (MT == 1 ? 3 : 2); ++i) {
+                const int waves = (tiles + ctas_per_sm[i] * sms - 1) / (ctas_per_sm[i] * sms);
+                if (waves < best_waves) { best_waves = waves; variant = shape[i]; }
+            }
+            if (MT == 1 && variant == 1 && K >= 8192) variant = 3;   // few tiles and a deep K: more warps per tile
         }
     }
     if (variant == 3 && MT != 1) variant = 1;
