@@ -26,8 +26,9 @@ def _pow2_at_least(n: int) -> int:
 
 
 class DecodeGraph:
-    def __init__(self, runner, num_requests: int, split_keys: tuple, splits_bound: int):
+    def __init__(self, runner, num_requests: int, split_keys: tuple, splits_bound: int, pool=None, logits_out=None):
         self.runner = runner
+        self.pool = pool
         self.num_requests = num_requests
         self.splits_bound = splits_bound
         device = runner.runtime.device
@@ -42,6 +43,7 @@ class DecodeGraph:
         self.ctx.error_count = torch.zeros(1, dtype=torch.int32, device=device)
         self.ctx.splits_bound = splits_bound
         self.ctx.split_keys = dict(split_keys)
+        self.ctx.logits_out = logits_out
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
 
@@ -84,7 +86,7 @@ class DecodeGraph:
             collecting = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(graph):
+                with torch.cuda.graph(graph, pool=self.pool):
                     self.logits = model.forward(self.ctx)
             finally:
                 if collecting:
@@ -106,6 +108,11 @@ class DecodeGraphs:
         self.graphs: dict = {}
         self.recordings = 0            # steps recorded so far, and the host time that took
         self.record_seconds = 0.0
+        # Recorded steps run one at a time, so they share one memory pool for what they allocate while being recorded
+        # and one home for their logits (valid until the next recorded step runs): the memory of the recordings is
+        # that of the largest one, not their sum (a [batch, vocabulary] float32 tensor for every batch size otherwise).
+        self.pool = None
+        self.logits_out = None
 
     def eligible(self, segments) -> bool:
         """A step of single tokens, each wanting its logits, of a model whose parts all allow recording
@@ -139,7 +146,11 @@ class DecodeGraphs:
         if g is None:
             if len(self.graphs) >= self.max_graphs:
                 self.graphs.pop(next(iter(self.graphs)))
-            g = DecodeGraph(self.runner, *key)
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+                self.logits_out = torch.empty((self.runner.cache.max_slots, self.runner.model.spec.vocab_size),
+                                              dtype=torch.float32, device=self.runner.runtime.device)
+            g = DecodeGraph(self.runner, *key, pool=self.pool, logits_out=self.logits_out)
             self.graphs[key] = g
         fresh = g.graph is None
         logits = g.run(segments, tokens_from)

@@ -680,19 +680,24 @@ def small_m_usable(rows: int, K: int, weight: torch.Tensor) -> bool:
 
 
 def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, residual: torch.Tensor | None = None,
-           next_norm: tuple | None = None):
+           next_norm: tuple | None = None, out: torch.Tensor | None = None):
     """y = x W^T with W [out, in] (src/layer/linear.cpp:213).  A bfloat16 weight runs on tensor cores with
     32-bit accumulation: up to SMALL_M_ROWS rows on the weight-streaming kernel, more on cuBLAS.  A float32
     weight runs on the fp32-FMA kernel, whatever the activation dtype.
     ``x`` may be ``NormedRows``: the weight-streaming kernel finishes the norm itself, otherwise it is computed
     first.  ``residual`` (float32 [rows, out]): where the weight-streaming kernel runs, y is added to it in
     place and None is returned - or, with ``next_norm`` = (weight, eps, owner) of the RMSNorm that follows, the
-    ``NormedRows`` that its consumer takes; otherwise y is returned and the caller adds it."""
+    ``NormedRows`` that its consumer takes; otherwise y is returned and the caller adds it.
+    ``out`` ([rows, out] of ``out_dtype``, contiguous; plain bfloat16-weight products only): where y is written."""
+    if out is not None and (residual is not None or tuple(out.shape) != (x.shape[0], weight.shape[0])
+                            or not out.is_contiguous() or weight.dtype != torch.bfloat16
+                            or out.dtype != (out_dtype or torch.bfloat16)):
+        raise KernelError("linear: `out` goes with a plain bfloat16-weight product and must be [rows, out] of the output dtype")
     if isinstance(x, NormedRows):
         sc = x.scaled
         if (x._value is None and small_m_usable(sc.shape[0], sc.shape[1], weight) and residual is None
                 and (out_dtype or torch.bfloat16) in (torch.bfloat16, torch.float32)):
-            return gemm_small_m(sc, weight, out_dtype or torch.bfloat16, row_ssq=(x.partials, x.eps))
+            return gemm_small_m(sc, weight, out_dtype or torch.bfloat16, out=out, row_ssq=(x.partials, x.eps))
         x = x.materialize()
     _need_cuda(x, weight)
     out_dtype = out_dtype or x.dtype
@@ -711,9 +716,11 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, residu
                 return NormedRows(residual, nw, eps, out_dtype, scaled, partials, owner)
             gemm_small_m(xb, weight, torch.float32, residual=residual)
             return None
-        return gemm_small_m(xb, weight, out_dtype)
+        return gemm_small_m(xb, weight, out_dtype, out=out)
     if out_dtype == torch.bfloat16:
-        return torch.mm(xb, weight.t())
+        return torch.mm(xb, weight.t(), out=out) if out is not None else torch.mm(xb, weight.t())
+    if out is not None:
+        return torch.mm(xb, weight.t(), out_dtype=torch.float32, out=out)
     return torch.mm(xb, weight.t(), out_dtype=torch.float32)
 
 

@@ -69,4 +69,7 @@ class LMHead(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if self.weight is None:
             raise RuntimeError("lm_head is not initialized")  # model.cpp:1373
-        return ops.linear(x, self.weight, torch.float32)
+        # a step whose logits have a fixed home (recorded steps share one) writes them there
+        home = getattr(ctx, "logits_out", None)
+        out = home[:x.shape[0]] if home is not None and self.weight.dtype == torch.bfloat16 else None
+        return ops.linear(x, self.weight, torch.float32, out=out)
