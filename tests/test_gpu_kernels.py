@@ -364,6 +364,47 @@ def test_attention_decode_spans_of_unequal_requests(nq, nkv, d, page, window, sp
         assert int(ws.count.abs().sum().item()) == 0
 
 
+@pytest.mark.parametrize("seed", list(range(24)))
+def test_attention_decode_spans_random_steps(seed, monkeypatch):
+    """Random decode steps for the tcgen05 decode kernel: 1 to 24 requests of 1 to 3,000 keys (many short ones, a few
+    long ones), 1 to 8 kv heads with groups of 1 to 16, both head sizes, every page size, with and without a window,
+    random span and cost settings - against the dense reference, on one workspace per head size that every case of
+    the run shares."""
+    dev, ops = need_gpu(), _ops()
+    rng = np.random.RandomState(1000 + seed)
+    d = int(rng.choice([64, 128]))
+    page = int(rng.choice([8, 16, 32, 64]))
+    nkv = int(rng.choice([1, 2, 3, 8]))
+    group = int(rng.choice([1, 2, 4, 5, 8, 16]))
+    if nkv * group > 32:
+        group = 4
+    nq = nkv * group
+    window = None if rng.rand() < 0.5 else int(rng.randint(100, 3000))
+    count = int(rng.randint(1, 25))
+    lengths = [int(rng.randint(1, 3001)) if rng.rand() < 0.3 else int(rng.randint(1, 200)) for _ in range(count)]
+    monkeypatch.setattr(ops.kernels, "DECODE_SPAN_MIN", int(rng.choice([1, 2, 4])))
+    monkeypatch.setattr(ops.kernels, "DECODE_PAIR_COST", int(rng.choice([0, 1, 2, 4])))
+    ws = _SHARED_DECODE_WS.get(d)
+    if ws is None:
+        ws = _SHARED_DECODE_WS[d] = ops.attention_decode_workspace(d, dev)
+        ws.acc.fill_(float("nan")); ws.ml.fill_(float("nan"))
+    segs = [(i, n - 1, 1) for i, n in enumerate(lengths)]
+    order = rng.permutation(count)
+    segs = [segs[i] for i in order]                       # the step need not list its requests in slot order
+    longest = int(np.argmax(lengths))
+    spike = None
+    if lengths[longest] > 300:
+        lo = 0 if window is None else max(0, lengths[longest] - window)
+        spike = (longest, int(rng.randint(lo, lengths[longest] - 1)), int(rng.randint(0, nq)))
+    err = _attention_case(ops, dev, torch.bfloat16, "tcgen05", nq, nkv, d, page, window, segs, lengths, seed=seed, spike=spike,
+                          decode_ws=ws)
+    assert err < 0.03, (seed, nq, nkv, d, page, window, lengths, err)
+    assert int(ws.count.abs().sum().item()) == 0
+
+
+_SHARED_DECODE_WS: dict = {}
+
+
 @pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 8), (4, 1, 64, 128), (32, 8, 128, 16)])
 @pytest.mark.parametrize("window", [None, 130, 900])
 @pytest.mark.parametrize("shares", [2, 3, 7, 16])
