@@ -799,27 +799,16 @@ __device__ __forceinline__ void fd_write_new_token(const FdParams& p, const FdIt
 
 // The pieces of a cut pair, added up in the order of their keys by the 128 softmax threads (thread = element of the
 // head).  Piece i lies in the scratch of CTA cta_first + i: slot 1 there for the first one, slot 0 for the others.
-// The loads of a chunk of pieces are issued together for all heads of the group: a chain of L2 latencies otherwise.
+// The loads of a chunk of pieces - maxima, sums and accumulators, for all heads of the group - are issued together
+// (a chain of L2 latencies otherwise) and the chunks are folded into running sums that are rescaled when a later
+// chunk brings a larger maximum: one pass over the scratch, the same arithmetic whatever the timing.
 template <int D, int GP>
 __device__ __forceinline__ void fd_merge(const FdParams& p, const FdItem& w, int tok, int tid, int G) {
     constexpr int PC = 32 / GP;          // pieces per chunk
     const int e = tid < D ? tid : 0;
-    float mstar[GP], num[GP], den[GP];
+    float mrun[GP], num[GP], den[GP];
 #pragma unroll
-    for (int g = 0; g < GP; ++g) { mstar[g] = -INFINITY; num[g] = 0.0f; den[g] = 0.0f; }
-    for (int i0 = 0; i0 < w.pieces; i0 += PC) {
-        float m[PC][GP];
-#pragma unroll
-        for (int i = 0; i < PC; ++i) {
-            const size_t r = ((size_t)(w.cta_first + i0 + i) * 2 + (i0 + i == 0 ? 1 : 0)) * 16;
-#pragma unroll
-            for (int g = 0; g < GP; ++g) m[i][g] = (i0 + i < w.pieces && g < G) ? __ldcg(p.ws_ml + (r + g) * 2) : -INFINITY;
-        }
-#pragma unroll
-        for (int i = 0; i < PC; ++i)
-#pragma unroll
-            for (int g = 0; g < GP; ++g) mstar[g] = fmaxf(mstar[g], m[i][g]);
-    }
+    for (int g = 0; g < GP; ++g) { mrun[g] = -INFINITY; num[g] = 0.0f; den[g] = 0.0f; }
     for (int i0 = 0; i0 < w.pieces; i0 += PC) {
         float2 ml[PC][GP];
         float a[PC][GP];
@@ -834,13 +823,22 @@ __device__ __forceinline__ void fd_merge(const FdParams& p, const FdItem& w, int
             }
         }
 #pragma unroll
-        for (int i = 0; i < PC; ++i)
+        for (int g = 0; g < GP; ++g) {
+            float mnew = mrun[g];
 #pragma unroll
-            for (int g = 0; g < GP; ++g) {
-                const float f = mstar[g] == -INFINITY ? 0.0f : fa_ex2(ml[i][g].x - mstar[g]);      // -inf gives 0
+            for (int i = 0; i < PC; ++i) mnew = fmaxf(mnew, ml[i][g].x);
+            if (mnew == -INFINITY) continue;                       // nothing but masked keys so far
+            const float keep = fa_ex2(mrun[g] - mnew);              // -inf gives 0
+            num[g] *= keep;
+            den[g] *= keep;
+#pragma unroll
+            for (int i = 0; i < PC; ++i) {
+                const float f = fa_ex2(ml[i][g].x - mnew);
                 num[g] += f * a[i][g];
                 den[g] += f * ml[i][g].y;
             }
+            mrun[g] = mnew;
+        }
     }
     if (tid < D) {
 #pragma unroll
