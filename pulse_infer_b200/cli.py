@@ -152,12 +152,60 @@ def qwen3_infer(argv=None) -> int:
     return 0
 
 
+def _bench(engine, kind: str, prompts: list, max_new: list, args) -> int:
+    """``--bench``: time the given prompts through the engine instead of printing what it generates; one JSON line.
+    serve: the whole run, requests in to last token out.  prefill: until every request has its first token (prompt
+    tokens per second).  decode: from the step after the last prompt portion to the end (generated tokens per second
+    while nothing but single tokens is in flight).  The decode steps of all batch sizes are recorded beforehand
+    (``Engine.warm_up``), no request stops early, and the clock is read with the device idle."""
+    import torch
+    recorded = engine.warm_up()
+    if kind == "prefill":
+        max_new = [1] * len(prompts)
+    ids = [engine.add_request(p, m, temperature=args.temperature, seed=args.seed + i, ignore_eos=True)
+           for i, (p, m) in enumerate(zip(prompts, max_new))]
+    reqs = [engine.get_request(rid) for rid in ids]
+    steps0 = engine.get_stats().num_steps
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    already = 0
+    if kind == "decode":
+        while engine.has_work() and any(r.is_prefill() for r in reqs):
+            engine.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        already = sum(len(engine.get_result(rid)) for rid in ids)
+        steps0 = engine.get_stats().num_steps
+    engine.run_until_complete()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    generated = sum(len(engine.get_result(rid)) for rid in ids)
+    prompt_tokens = sum(len(p) for p in prompts)
+    st = engine.get_stats()
+    line = {"bench": kind, "requests": len(prompts), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+            "seconds": round(dt, 4), "steps": st.num_steps - steps0, "preemptions": st.num_preemptions,
+            "max_batch_size": args.max_batch_size, "chunk_size": args.chunk_size, "dtype": args.dtype,
+            "decode_steps_recorded_before": recorded}
+    if kind == "prefill":
+        line["prompt_tokens_per_s"] = round(prompt_tokens / dt, 1)
+    elif kind == "decode":
+        line["timed_tokens"] = generated - already
+        line["generated_tokens_per_s"] = round((generated - already) / dt, 1)
+    else:
+        line["generated_tokens_per_s"] = round(generated / dt, 1)
+        line["all_tokens_per_s"] = round((generated + prompt_tokens) / dt, 1)
+    print(json.dumps(line))
+    return 0
+
+
 def qwen3_continuous_batch_demo(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="qwen3_continuous_batch_demo", description="continuous batching, greedy")
     _common(ap)
     ap.add_argument("--max-batch-size", type=int, default=2)
     ap.add_argument("--chunk-size", type=int, default=64)
     ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--bench", choices=["decode", "prefill", "serve"], default=None,
+                    help="time the prompts through the engine (one JSON line) instead of printing the generated ids")
     args = ap.parse_args(argv)
     cfg = _config_first(args)
     prompts = _prompts(args, cfg.vocab_size)
@@ -168,6 +216,8 @@ def qwen3_continuous_batch_demo(argv=None) -> int:
     estimate = sum(len(p) + m + 16 for p, m in zip(prompts, max_new))
     num_pages = args.num_pages or (None if args.kv_gb else max(64, (estimate + args.page_size - 1) // args.page_size))
     engine, _ = _make_engine(args, args.max_batch_size, args.chunk_size, num_pages, None)
+    if args.bench:
+        return _bench(engine, args.bench, prompts, max_new, args)
     topk = _topk_recorder(engine, args.print_logits_topk) if args.print_logits_topk > 0 else None
     ids = [engine.add_request(p, m, temperature=args.temperature, seed=args.seed + i, ignore_eos=args.ignore_eos)
            for i, (p, m) in enumerate(zip(prompts, max_new))]

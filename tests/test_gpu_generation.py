@@ -201,6 +201,25 @@ def test_command_line_programs(model_folders, tmp_path):
         assert [t for t, _ in top] == [int(i) for i in np.argsort(-row, kind="stable")[:3]]
         assert abs(top[0][1] - row[tok]) <= 2e-5 * np.abs(row).max() + 1e-5
         toks.append(tok)
+    # --bench: the same prompts timed instead of printed, one JSON line per kind
+    for kind in ("serve", "prefill", "decode"):
+        out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen3_continuous_batch_demo"), model_folders["D"],
+                              "--prompt-len", "40", "--prompt-len", "9", "--prompt-len", "70", "--max-new-tokens", "12",
+                              "--max-batch-size", "3", "--chunk-size", "32", "--bench", kind],
+                             capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, out.stderr[-2000:]
+        recs = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+        assert len(recs) == 1
+        rec = recs[0]
+        assert rec["bench"] == kind and rec["requests"] == 3 and rec["prompt_tokens"] == 119 and rec["seconds"] > 0
+        assert rec["decode_steps_recorded_before"] == 3 and rec["preemptions"] == 0
+        if kind == "serve":
+            assert rec["generated_tokens"] == 36 and rec["generated_tokens_per_s"] > 0 and rec["all_tokens_per_s"] > rec["generated_tokens_per_s"]
+        elif kind == "prefill":
+            assert rec["generated_tokens"] == 3 and rec["prompt_tokens_per_s"] > 0
+        else:
+            # timed from the step after the last prompt portion: the tokens sampled by then are not counted
+            assert rec["generated_tokens"] == 36 and 30 <= rec["timed_tokens"] <= 35 and rec["steps"] <= 12
 
 
 # ---- each part of a layer alone ----------------------------------------------------------------------------
