@@ -75,6 +75,21 @@ class Engine:
         self.engine.abort(request_id)
 
     # ---- convenience ---------------------------------------------------------------------------------------
+    def run(self) -> dict:
+        """Run until no request is left; returns {request id: generated ids} of every request that has finished."""
+        self.run_until_complete()
+        return {rid: req.resolved_tokens() for rid, req in self.engine.scheduler.request_map.items() if req.is_finished()}
+
+    def replay(self, trace) -> dict:
+        """Feed given token ids through this engine's own step function, step by step, sampling nothing: ``trace`` is
+        a list of steps ``{"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}``
+        (dicts or JSON strings, as ``bin/trace_run`` reads them); returns {step: float32 logits [wanted, vocab]} for
+        the steps in which something was wanted.  The engine must be idle, and the trace's ids its own."""
+        from .engine.replay import replay_steps
+        if self.has_work():
+            raise RuntimeError("replay needs an engine without requests in flight")
+        return {step_id: logits for step_id, _, logits in replay_steps(self.runner, trace) if logits is not None}
+
     def warm_up(self, batch_sizes=None) -> int:
         """Records the decode step of every batch size up to ``max_batch_size`` (or of ``batch_sizes``) before traffic
         arrives, as a server does at start-up.  Recording a step takes tens of milliseconds the first time a batch size

@@ -25,6 +25,38 @@ TOKEN_ROUNDING = 64      # a request's token count is rounded up to this when si
 MAX_LIVE_REQUESTS = 8    # default number of request slots
 
 
+def replay_steps(runner, steps):
+    """The steps of a trace through a runner's step function, one after the other: yields (step id, the step's
+    segments, float32 logits [wanted, vocab] as a numpy array or None when nothing was wanted).  ``steps``: JSON
+    strings or dicts of the form shown above.  Requests are opened at their first tokens and closed where ``end``
+    names them."""
+    for step in steps:
+        if isinstance(step, str):
+            step = step.strip()
+            if not step:
+                continue
+            step = json.loads(step)
+        step_id = step["step"]
+        segments = []
+        for entry in step.get("entries", []):
+            rid = entry["id"]
+            if not entry.get("tokens"):
+                continue                      # an entry without tokens asks for nothing
+            if not runner.cache.has(rid):
+                runner.open(rid)
+            segments.append(Segment(rid, [int(t) for t in entry["tokens"]], [int(w) for w in entry.get("want", [])]))
+        arr = None
+        if segments:
+            logits = runner.step(segments)
+            runner.check_device_errors()
+            if logits.shape[0] > 0:
+                arr = logits.detach().to("cpu", torch.float32).numpy()
+        for rid in step.get("end", []):
+            if runner.cache.has(rid):
+                runner.close(rid)
+        yield step_id, segments, arr
+
+
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int | None, lines, device="cuda:0", log=None,
            page_size: int = PAGE_SIZE, num_pages: int | None = None, max_requests: int = MAX_LIVE_REQUESTS) -> int:
     """Run the steps read from ``lines`` (an iterable of JSON strings); returns the number of steps.
@@ -46,34 +78,14 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int | None, lin
     out = log or sys.stdout
     count = 0
     index = []
-    for line in lines:
-        line = line.strip()
-        if not line:
-            continue
-        obj = json.loads(line)
-        step_id = obj["step"]
-        segments = []
-        for entry in obj.get("entries", []):
-            rid = entry["id"]
-            if not entry.get("tokens"):
-                continue                      # an entry without tokens asks for nothing
-            if not runner.cache.has(rid):
-                runner.open(rid)
-            segments.append(Segment(rid, [int(t) for t in entry["tokens"]], [int(w) for w in entry.get("want", [])]))
-        if segments:
-            logits = runner.step(segments)
-            runner.check_device_errors()
-            if logits.shape[0] > 0:
-                arr = logits.detach().to("cpu", torch.float32).numpy().astype("<f4", copy=False)
-                arr.tofile(os.path.join(out_dir, f"{step_id}.f32"))
-                row = 0
-                for seg in segments:
-                    for w in seg.want:
-                        index.append({"step": step_id, "request": seg.request_id, "position": seg.start + w, "row": row})
-                        row += 1
-        for rid in obj.get("end", []):
-            if runner.cache.has(rid):
-                runner.close(rid)
+    for step_id, segments, logits in replay_steps(runner, lines):
+        if logits is not None:
+            logits.astype("<f4", copy=False).tofile(os.path.join(out_dir, f"{step_id}.f32"))
+            row = 0
+            for seg in segments:
+                for w in seg.want:
+                    index.append({"step": step_id, "request": seg.request_id, "position": seg.start + w, "row": row})
+                    row += 1
         print(f"done {step_id}", file=out, flush=True)
         count += 1
     with open(os.path.join(out_dir, "index.json"), "w", encoding="utf-8") as fh:

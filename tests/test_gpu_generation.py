@@ -121,6 +121,34 @@ def test_warm_up_records_every_batch_size_once(model_folders):
     assert no_graphs.warm_up() == 0
 
 
+def test_engine_run_and_replay_through_the_python_entry_point(model_folders):
+    """``Engine.run()`` returns what every request generated; ``Engine.replay(trace)`` feeds given ids through the same
+    engine's step function and returns the logits at the wanted places - those of the plain implementation, whatever
+    the cut - and leaves the engine ready to generate."""
+    need_gpu()
+    from pulse_infer_b200 import Engine
+    folder, cfg = model_folders["B"], CONFIGS["B"]
+    pc, pw = load_plain(folder)
+    engine = Engine(folder, dtype="float32", page_size=16, num_pages=24, max_batch_size=3, chunk_size=16)
+    a, b = random_tokens(71, 37, cfg.vocab_size), random_tokens(72, 12, cfg.vocab_size)
+    trace = [{"step": 0, "entries": [{"id": "a", "tokens": a[:20], "want": [19]}, {"id": "b", "tokens": b[:5], "want": []}]},
+             json.dumps({"step": 1, "entries": [{"id": "a", "tokens": a[20:22], "want": [0, 1]}, {"id": "b", "tokens": b[5:], "want": [6]}], "end": ["b"]}),
+             {"step": 2, "entries": [{"id": "a", "tokens": a[22:], "want": [14]}], "end": ["a"]},
+             {"step": 3, "entries": [], "end": []}]
+    got = engine.replay(trace)
+    assert sorted(got) == [0, 1, 2]
+    wa, wb = plain_model.forward(pc, pw, a), plain_model.forward(pc, pw, b)
+    for step, want in ((0, wa[[19]]), (1, np.concatenate([wa[[20, 21]], wb[[11]]])), (2, wa[[36]])):
+        assert got[step].shape == want.shape and got[step].dtype == np.float32
+        assert np.abs(got[step] - want).max() <= 2e-5 * np.abs(want).max()
+    assert engine.runner.cache.free_pages() == [24] * len(engine.runner.cache.free_pages())
+    ids = [engine.add_request(p, 5, ignore_eos=True) for p in (a[:9], b)]
+    with pytest.raises(RuntimeError):
+        engine.replay(trace)                                  # requests in flight
+    done = engine.run()
+    assert done == {ids[0]: _plain_generate(pc, pw, a[:9], 5), ids[1]: _plain_generate(pc, pw, b, 5)}
+
+
 def test_generation_survives_preemption_and_eos(model_folders):
     """So few pages that requests are preempted and recomputed; tokens are the same as with plenty."""
     need_gpu()
