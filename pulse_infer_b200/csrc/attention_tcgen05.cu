@@ -921,8 +921,10 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // ring, queries and probabilities start as zeros: rows that nothing fills (keys past the end of a range,
-    // query rows past the group) must not hold NaN bit patterns
+    // ring, queries and probabilities start as zeros: rows that nothing fills (keys past the end of a pair's last tile,
+    // query rows past the group) must not hold NaN bit patterns - a probability of exactly zero times a NaN is a NaN.
+    // (Clearing only the value rows behind a pair's end, in the softmax threads, instead of the whole ring measured
+    // the same step time.)
     for (unsigned i = threadIdx.x; i < (STAGES * STAGE_BYTES + 2 * QBUF_BYTES + 2 * PHALF_BYTES) / 16; i += FD_THREADS)
         reinterpret_cast<uint4*>(sKV)[i] = make_uint4(0, 0, 0, 0);
     pdl_wait();
@@ -1252,6 +1254,24 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
+
+#ifdef FD_POISON_TEST
+// Test builds only: every SM's shared memory is filled with NaN bit patterns, so that a kernel that reads shared
+// memory it has not written shows it in its results.
+__global__ void fd_poison_shared_kernel(unsigned bytes) {
+    extern __shared__ unsigned char poison_smem[];
+    for (unsigned i = threadIdx.x; i < bytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(poison_smem)[i] = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+    __syncthreads();
+    if (reinterpret_cast<volatile unsigned*>(poison_smem)[threadIdx.x] != 0xFFFFFFFFu) __nanosleep(1);      // keeps the stores
+}
+PI_EXPORT int pi_attention_tcgen05_test_poison_shared(cudaStream_t stream) {
+    const unsigned bytes = 227 * 1024;
+    cudaError_t err = cudaFuncSetAttribute(fd_poison_shared_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (err != cudaSuccess) return (int)err;
+    fd_poison_shared_kernel<<<4 * pi_sm_count(), 256, bytes, stream>>>(bytes);
+    return pi_check_launch("pi_attention_tcgen05_test_poison_shared");
+}
+#endif
 
 // ---- host side ---------------------------------------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 fa_encode_fn() {

@@ -181,7 +181,10 @@ def _attention_case(ops, dev, dtype, impl, nq, nkv, d, page, window, segs, lengt
     for (slot, start, n), off in zip(segs, meta["seg_off"].tolist()):
         want = dense_attention(q[off:off + n].double(), kv.k_dense[slot], kv.v_dense[slot],
                                list(range(start, start + n)), window, scale)
-        worst = max(worst, float((out[off:off + n] - want).abs().max()))
+        err = float((out[off:off + n] - want).abs().max())
+        if not math.isfinite(err):
+            return float("inf")               # max() would drop a NaN
+        worst = max(worst, err)
     return worst
 
 
@@ -362,6 +365,63 @@ def test_attention_decode_spans_of_unequal_requests(nq, nkv, d, page, window, sp
                               spike=spike, decode_ws=ws)
         assert err < 0.03, (call, err)
         assert int(ws.count.abs().sum().item()) == 0
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (12, 3, 64, 8), (16, 1, 64, 64)])
+@pytest.mark.parametrize("fused", [False, True])
+def test_attention_decode_reads_no_shared_memory_it_has_not_written(nq, nkv, d, page, fused, monkeypatch):
+    """The pages behind the end of a request's last key tile are never loaded into the decode kernel's ring, and what
+    lies there in shared memory must not reach the output (a probability of exactly zero times a NaN is a NaN).  A test
+    build of the library fills every SM's shared memory with NaN bit patterns right before the kernel runs; requests
+    whose lengths end anywhere in a tile - one key, a page, a tile less one, several tiles and a bit - must still give
+    the reference's output.  (Checked once that a kernel which neither clears its ring nor those rows fails here.)"""
+    import ctypes
+    dev, ops = need_gpu(), _ops()
+    from pulse_infer_b200.csrc import build
+    monkeypatch.setenv("PULSE_NVCC_FLAGS", "-DFD_POISON_TEST")
+    test_lib = ctypes.CDLL(build.library_path("attention_tcgen05", d))
+    monkeypatch.delenv("PULSE_NVCC_FLAGS")
+    lengths = [1, page, page + 1, 127, 128, 129, 200, 383, 700, 1025]
+    segs = [(i, n - 1, 1) for i, n in enumerate(lengths)]
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for window in (None, 150):
+        if fused:
+            kv = PagedKV(lengths, nkv, d, page, torch.bfloat16, dev, seed=d + page, fill_garbage=False)
+            meta = segments_to_device(segs, dev)
+            T = meta["T"]
+            g = torch.Generator().manual_seed(page)
+            qkv = torch.randn(T, (nq + 2 * nkv) * d, generator=g).to(torch.bfloat16).to(dev)
+            err = torch.zeros(1, dtype=torch.int32, device=dev)
+            k1, v1, q1 = kv.kcache.clone(), kv.vcache.clone(), qkv.clone()
+            ops.qk_norm_rope_write(q1, None, None, 1e-6, None, None, True, k1, v1, kv.table_dev, meta["token_slot"],
+                                   meta["positions"], page, nq, nkv, d, err)
+            splits = max(ops.attention_num_splits(st, window, 256) for _, st, _ in segs)
+            acc = torch.empty(T * nq * splits * d, dtype=torch.float32, device=dev)
+            ml = torch.empty(T * nq * splits * 2, dtype=torch.float32, device=dev)
+            want = ops.attention_mma(q1, q1.shape[1], k1, v1, kv.table_dev, meta["seg_off"], meta["seg_slot"], meta["seg_start"],
+                                     meta["seg_len"], meta["token_seg"], T, T, 1, False, True, splits, acc, ml, nq, nkv, d, page,
+                                     window, 1.0 / math.sqrt(d), split_keys=256, decode_on_tcgen05=False)
+            ws = ops.attention_decode_workspace(d, dev)
+            assert test_lib.pi_attention_tcgen05_test_poison_shared(stream) == 0
+            torch.cuda.synchronize()
+            got = ops.attention_decode_fused(qkv.clone(), kv.kcache.clone(), kv.vcache.clone(), kv.table_dev, meta["seg_off"],
+                                             meta["seg_slot"], meta["seg_start"], meta["seg_len"], T, nq, nkv, d, page, window,
+                                             1.0 / math.sqrt(d), None, None, 1e-6, None, None, err, workspace=ws)
+            assert torch.isfinite(got.float()).all()
+            assert float((got.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max()) + 1e-3
+        else:
+            orig = ops.kernels.attention_mma
+
+            def poisoned(*a, **kw):
+                orig(*a, **kw)                                     # libraries loaded, workspace kernels out of the way
+                assert test_lib.pi_attention_tcgen05_test_poison_shared(stream) == 0
+                torch.cuda.synchronize()
+                return orig(*a, **kw)
+            monkeypatch.setattr(ops, "attention_mma", poisoned)
+            err = _attention_case(ops, dev, torch.bfloat16, "tcgen05", nq, nkv, d, page, window, segs, lengths, seed=3)
+            monkeypatch.setattr(ops, "attention_mma", orig)
+            assert err < 0.03, err                     # NaN compares false
+    assert ops.attention_tcgen05_status(d) == 0
 
 
 @pytest.mark.parametrize("seed", list(range(24)))
